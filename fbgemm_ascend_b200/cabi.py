@@ -1,0 +1,146 @@
+"""ctypes view of the C ABI in ``include/tbe_b200.h`` for callers holding torch tensors.
+
+The torch operators go through the same entry points from C++; this module exists for
+callers that need arguments the operator schema does not have (destination scatter,
+column remap, error flag) and for tests that exercise the boundary directly.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional, Sequence
+
+import torch
+
+from .types import PoolingMode, SparseType
+
+_vp, _i64, _i32 = C.c_void_p, C.c_int64, C.c_int32
+
+
+class LookupArgs(C.Structure):
+    """Mirror of ``tbe_b200_lookup_args`` (field order and types must match the header)."""
+    _fields_ = [
+        ("dev_weights", _vp), ("dev_weights_bytes", _i64), ("weights_offsets", _vp), ("weights_tys", _vp),
+        ("D_offsets", _vp), ("T", _i32), ("B", _i64), ("total_D", _i64), ("max_D", _i32), ("indices", _vp),
+        ("offsets", _vp), ("index_bits", _i32), ("num_indices", _i64), ("indice_weights", _vp),
+        ("pooling_mode", _i32), ("output_dtype", _i32), ("row_alignment", _i32), ("fp8_exponent_bits", _i32),
+        ("fp8_exponent_bias", _i32), ("output", _vp), ("output_stride", _i64), ("output_col_offsets", _vp),
+        ("dest_outputs", _vp), ("rows_per_dest", _i64), ("error_flag", _vp),
+    ]
+
+
+EXPORTS = {
+    "tbe_b200_int_nbit_lookup": (_i32, [C.POINTER(LookupArgs), _vp]),
+    "tbe_b200_quantize_8bit_rowwise": (_i32, [_vp, _i32, _i64, _i64, _vp, _vp]),
+    "tbe_b200_dequantize_8bit_rowwise": (_i32, [_vp, _i64, _i64, _vp, _i32, _vp]),
+    "tbe_b200_quantize_nbit_rowwise_sbhalf": (_i32, [_i32, _vp, _i64, _i64, _vp, _vp]),
+    "tbe_b200_dequantize_nbit_rowwise_sbhalf": (_i32, [_i32, _vp, _i64, _i64, _vp, _vp]),
+    "tbe_b200_pack_table_rows": (_i32, [_i32, _vp, _i64, _i64, _i64, _vp, _vp]),
+    "tbe_b200_quantize_to_table_rows": (_i32, [_i32, _vp, _i64, _i64, _i64, _vp, _vp]),
+    "tbe_b200_permute_pooled_embs": (_i32, [_vp, _i64, _i64, _i32, _i64, _i64, _vp, _vp, _vp, _i32, _vp, _vp, _vp]),
+    "tbe_b200_last_error": (C.c_char_p, []),
+    "tbe_b200_version": (_i32, []),
+}
+
+_lib = None
+
+
+def lib():
+    """The loaded ``libtbe_b200.so`` with argument types declared."""
+    global _lib
+    if _lib is None:
+        from . import cabi_lib
+        for name, (res, args) in EXPORTS.items():
+            fn = getattr(cabi_lib, name)
+            fn.restype = res
+            fn.argtypes = args
+        _lib = cabi_lib
+    return _lib
+
+
+def last_error() -> str:
+    return lib().tbe_b200_last_error().decode()
+
+
+def check(rc: int, what: str) -> None:
+    if rc != 0:
+        raise RuntimeError(f"{what} failed (status {rc}): {last_error()}")
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return None if t is None else t.data_ptr()
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+_OUT_DTYPE = {torch.float32: SparseType.FP32, torch.float16: SparseType.FP16, torch.bfloat16: SparseType.BF16}
+
+
+def lookup(dev_weights: torch.Tensor, weights_offsets: torch.Tensor, weights_tys: torch.Tensor,
+           D_offsets: torch.Tensor, total_D: int, max_D: int, indices: torch.Tensor, offsets: torch.Tensor,
+           pooling_mode: int, output: torch.Tensor, indice_weights: Optional[torch.Tensor] = None,
+           row_alignment: int = 16, fp8_exponent_bits: int = 4, fp8_exponent_bias: int = 7,
+           output_stride: Optional[int] = None, output_col_offsets: Optional[torch.Tensor] = None,
+           dest_outputs: Optional[torch.Tensor] = None, rows_per_dest: int = 0,
+           error_flag: Optional[torch.Tensor] = None, B: Optional[int] = None) -> torch.Tensor:
+    """``tbe_b200_int_nbit_lookup`` on the current stream, writing into ``output``.
+
+    ``dest_outputs`` is an int64 CUDA tensor of base addresses (one per ``rows_per_dest`` rows of
+    the batch); ``output_col_offsets`` an int64 CUDA tensor [T].  All tensors must be contiguous
+    and on the current device; nothing is copied or converted here.
+    """
+    T = weights_offsets.numel()
+    assert weights_offsets.dtype == torch.int64 and weights_tys.dtype == torch.uint8 and D_offsets.dtype == torch.int32
+    assert indices.dtype in (torch.int32, torch.int64) and offsets.dtype == indices.dtype
+    a = LookupArgs()
+    a.dev_weights = _ptr(dev_weights)
+    a.dev_weights_bytes = dev_weights.numel()
+    a.weights_offsets = _ptr(weights_offsets)
+    a.weights_tys = _ptr(weights_tys)
+    a.D_offsets = _ptr(D_offsets)
+    a.T = T
+    a.B = (offsets.numel() - 1) // T if B is None else B
+    a.total_D = total_D
+    a.max_D = max_D
+    a.indices = _ptr(indices)
+    a.offsets = _ptr(offsets)
+    a.index_bits = 32 if indices.dtype == torch.int32 else 64
+    a.num_indices = indices.numel()
+    a.indice_weights = _ptr(indice_weights)
+    a.pooling_mode = int(pooling_mode)
+    a.output_dtype = int(_OUT_DTYPE[output.dtype])
+    a.row_alignment = row_alignment
+    a.fp8_exponent_bits = fp8_exponent_bits
+    a.fp8_exponent_bias = fp8_exponent_bias
+    a.output = _ptr(output)
+    if output_stride is None:
+        output_stride = max_D if int(pooling_mode) == int(PoolingMode.NONE) else total_D
+    a.output_stride = output_stride
+    a.output_col_offsets = _ptr(output_col_offsets)
+    a.dest_outputs = _ptr(dest_outputs)
+    a.rows_per_dest = rows_per_dest
+    a.error_flag = _ptr(error_flag)
+    check(lib().tbe_b200_int_nbit_lookup(C.byref(a), _stream()), "tbe_b200_int_nbit_lookup")
+    return output
+
+
+def permute_pooled_embs(pooled: torch.Tensor, offset_dim_list: torch.Tensor, permute_list: torch.Tensor,
+                        inv_offset_dim_list: torch.Tensor, output: torch.Tensor,
+                        error_flag: Optional[torch.Tensor] = None) -> torch.Tensor:
+    total_D = pooled.shape[-1]
+    B = pooled.numel() // total_D
+    check(lib().tbe_b200_permute_pooled_embs(_ptr(pooled), B, total_D, pooled.element_size(), pooled.stride(-2),
+                                             output.stride(-2), _ptr(offset_dim_list), _ptr(permute_list),
+                                             _ptr(inv_offset_dim_list), permute_list.numel(), _ptr(output),
+                                             _ptr(error_flag), _stream()), "tbe_b200_permute_pooled_embs")
+    return output
+
+
+def quantize_to_table_rows(x: torch.Tensor, weight_ty: int, row_bytes_: int, rows_out: torch.Tensor) -> torch.Tensor:
+    """fp32 [E, D] -> table rows written in place into ``rows_out`` (uint8, E*row_bytes bytes)."""
+    assert x.dtype == torch.float32 and x.is_contiguous() and rows_out.dtype == torch.uint8
+    assert rows_out.numel() >= x.shape[0] * row_bytes_
+    check(lib().tbe_b200_quantize_to_table_rows(int(weight_ty), _ptr(x), x.shape[0], x.shape[1], row_bytes_,
+                                                _ptr(rows_out), _stream()), "tbe_b200_quantize_to_table_rows")
+    return rows_out

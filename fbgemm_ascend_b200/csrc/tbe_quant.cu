@@ -1,0 +1,422 @@
+// Rowwise quantizers / dequantizers and table-row packing for B200.
+//
+//   FloatToFused8BitRowwiseQuantized / Fused8BitRowwiseQuantizedToFloat
+//   FloatToFusedNBitRowwiseQuantizedSBHalf / FusedNBitRowwiseQuantizedSBHalfToFloat
+//
+// These operators are not defined in the reference tree; it inherits them from
+// fbgemm_gpu (fbgemm_ascend/__init__.py:9).  Their byte layout must be bit-exact,
+// so the arithmetic below is written without fused multiply-adds where the CPU
+// definition has none, with IEEE division, and with round-to-nearest-even.
+//
+// All kernels are HBM-bound streaming passes: a group of LPR lanes owns a row,
+// finds min/max with shuffles (first pass over the row), then re-reads the row
+// (L1/L2-resident by then) and writes the codes.
+#include "tbe_common.cuh"
+
+namespace tbe {
+namespace {
+
+constexpr unsigned kFull = 0xffffffffu;
+constexpr int kThreads = 256;
+
+template <typename InT>
+__device__ __forceinline__ float load_in(const InT* p);
+template <>
+__device__ __forceinline__ float load_in<float>(const float* p) { return __ldg(p); }
+template <>
+__device__ __forceinline__ float load_in<__half>(const __half* p) { return __half2float(__ldg(p)); }
+
+template <int LPR>
+__device__ __forceinline__ void group_minmax(float& mn, float& mx)
+{
+#pragma unroll
+    for (int d = LPR / 2; d >= 1; d >>= 1) {
+        mn = fminf(mn, __shfl_xor_sync(kFull, mn, d));
+        mx = fmaxf(mx, __shfl_xor_sync(kFull, mx, d));
+    }
+}
+
+// Row min/max over D elements, LPR lanes per row.  The comparisons reproduce a
+// sequential `if (x < mn) mn = x` scan for finite inputs.
+template <int LPR, typename InT>
+__device__ __forceinline__ void row_minmax(const InT* x, int64_t D, int k, bool vec4, float& mn, float& mx)
+{
+    mn = __int_as_float(0x7f800000);
+    mx = __int_as_float(0xff800000);
+    if (vec4) {
+        const float4* x4 = reinterpret_cast<const float4*>(x);
+        for (int64_t v = k; v < D / 4; v += LPR) {
+            const float4 f = __ldg(x4 + v);
+            mn = fminf(fminf(mn, f.x), fminf(f.y, fminf(f.z, f.w)));
+            mx = fmaxf(fmaxf(mx, f.x), fmaxf(f.y, fmaxf(f.z, f.w)));
+        }
+    } else {
+        for (int64_t c = k; c < D; c += LPR) {
+            const float f = load_in<InT>(x + c);
+            mn = fminf(mn, f);
+            mx = fmaxf(mx, f);
+        }
+    }
+    group_minmax<LPR>(mn, mx);
+    if (D == 0) { mn = 0.0f; mx = 0.0f; }
+}
+
+// ---- 8-bit -------------------------------------------------------------------
+//
+// TABLE == false: out row = [D codes][fp32 scale][fp32 bias], stride D + 8.
+// TABLE == true : out row = [fp16 scale][fp16 bias][D codes], stride row_bytes
+//                 (the table-batched layout), padding zeroed.
+template <int LPR, typename InT, bool TABLE>
+__global__ void __launch_bounds__(kThreads)
+quantize_8bit_kernel(const InT* __restrict__ in, int64_t N, int64_t D, uint8_t* __restrict__ out, int64_t out_stride)
+{
+    constexpr int RPB = kThreads / LPR;
+    const int k = threadIdx.x % LPR;
+    const int64_t r = static_cast<int64_t>(blockIdx.x) * RPB + threadIdx.x / LPR;
+    // Whole groups leave together (LPR divides 32), so shuffles below stay convergent per group;
+    // rows past N still run the shuffles with no memory access.
+    const bool live = r < N;
+    const InT* x = in + (live ? r : 0) * D;
+    const bool in_vec4 = sizeof(InT) == 4 && (D % 4 == 0) && ((reinterpret_cast<uintptr_t>(in) & 15) == 0);
+    float mn, mx;
+    row_minmax<LPR, InT>(x, live ? D : 0, k, in_vec4, mn, mx);
+    if (!live) return;
+    const float range = mx - mn;
+    const float scale = __fdiv_rn(range, 255.0f);
+    const float inv = __fdiv_rn(255.0f, __fadd_rn(range, 1e-8f));
+    uint8_t* o = out + r * out_stride;
+    uint8_t* codes = TABLE ? o + 4 : o;
+    const bool out_vec4 = in_vec4 && (out_stride % 4 == 0) && ((reinterpret_cast<uintptr_t>(out) & 3) == 0);
+    if (out_vec4) {
+        const float4* x4 = reinterpret_cast<const float4*>(x);
+        for (int64_t v = k; v < D / 4; v += LPR) {
+            const float4 f = __ldg(x4 + v);
+            const uint32_t q0 = static_cast<uint32_t>(__float2int_rn(__fmul_rn(__fsub_rn(f.x, mn), inv))) & 0xffu;
+            const uint32_t q1 = static_cast<uint32_t>(__float2int_rn(__fmul_rn(__fsub_rn(f.y, mn), inv))) & 0xffu;
+            const uint32_t q2 = static_cast<uint32_t>(__float2int_rn(__fmul_rn(__fsub_rn(f.z, mn), inv))) & 0xffu;
+            const uint32_t q3 = static_cast<uint32_t>(__float2int_rn(__fmul_rn(__fsub_rn(f.w, mn), inv))) & 0xffu;
+            *reinterpret_cast<uint32_t*>(codes + 4 * v) = q0 | (q1 << 8) | (q2 << 16) | (q3 << 24);
+        }
+    } else {
+        for (int64_t c = k; c < D; c += LPR) {
+            const float f = load_in<InT>(x + c);
+            codes[c] = static_cast<uint8_t>(__float2int_rn(__fmul_rn(__fsub_rn(f, mn), inv)));
+        }
+    }
+    if (TABLE) {
+        if (k == 0) {
+            const uint32_t h = f32_to_f16_bits(scale) | (f32_to_f16_bits(mn) << 16);
+            o[0] = h & 0xff; o[1] = (h >> 8) & 0xff; o[2] = (h >> 16) & 0xff; o[3] = (h >> 24) & 0xff;
+        }
+        for (int64_t c = 4 + D + k; c < out_stride; c += LPR) o[c] = 0;
+    } else if (k == 0) {
+        const uint32_t sb[2] = {__float_as_uint(scale), __float_as_uint(mn)};
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[D + j] = (sb[j >> 2] >> (8 * (j & 3))) & 0xff;
+    }
+}
+
+template <typename OutT>
+__device__ __forceinline__ void store_deq(OutT* p, float v);
+template <>
+__device__ __forceinline__ void store_deq<float>(float* p, float v) { *p = v; }
+template <>
+__device__ __forceinline__ void store_deq<__half>(__half* p, float v) { *p = __float2half_rn(v); }
+
+template <int LPR, typename OutT>
+__global__ void __launch_bounds__(kThreads)
+dequantize_8bit_kernel(const uint8_t* __restrict__ in, int64_t N, int64_t Dq, OutT* __restrict__ out)
+{
+    constexpr int RPB = kThreads / LPR;
+    const int k = threadIdx.x % LPR;
+    const int64_t r = static_cast<int64_t>(blockIdx.x) * RPB + threadIdx.x / LPR;
+    if (r >= N) return;
+    const int64_t D = Dq - 8;
+    const uint8_t* q = in + r * Dq;
+    uint32_t sb[2] = {0u, 0u};
+#pragma unroll
+    for (int j = 0; j < 8; ++j) sb[j >> 2] |= static_cast<uint32_t>(__ldg(q + D + j)) << (8 * (j & 3));
+    const float scale = __uint_as_float(sb[0]), bias = __uint_as_float(sb[1]);
+    OutT* o = out + r * D;
+    const bool vec = sizeof(OutT) == 4 && (Dq % 4 == 0) && ((reinterpret_cast<uintptr_t>(in) & 3) == 0) &&
+                     ((reinterpret_cast<uintptr_t>(out) & 15) == 0);
+    if (vec) {
+        for (int64_t v = k; v < D / 4; v += LPR) {
+            const uint32_t w = ldg4(q + 4 * v);
+            float4 f;
+            f.x = fmaf(static_cast<float>(w & 0xffu), scale, bias);
+            f.y = fmaf(static_cast<float>((w >> 8) & 0xffu), scale, bias);
+            f.z = fmaf(static_cast<float>((w >> 16) & 0xffu), scale, bias);
+            f.w = fmaf(static_cast<float>(w >> 24), scale, bias);
+            *reinterpret_cast<float4*>(reinterpret_cast<float*>(o) + 4 * v) = f;
+        }
+    } else {
+        for (int64_t c = k; c < D; c += LPR) store_deq<OutT>(o + c, fmaf(static_cast<float>(__ldg(q + c)), scale, bias));
+    }
+}
+
+// ---- 2- and 4-bit ------------------------------------------------------------
+//
+// TABLE == false: out row = [codes][fp16 scale][fp16 bias], stride pbytes + 4.
+// TABLE == true : out row = [fp16 scale][fp16 bias][codes], stride row_bytes.
+template <int LPR, int BITS, bool TABLE>
+__global__ void __launch_bounds__(kThreads)
+quantize_nbit_kernel(const float* __restrict__ in, int64_t N, int64_t D, uint8_t* __restrict__ out, int64_t out_stride)
+{
+    constexpr int RPB = kThreads / LPR;
+    constexpr int PER = 8 / BITS;
+    constexpr int QMAX = (1 << BITS) - 1;
+    const int k = threadIdx.x % LPR;
+    const int64_t r = static_cast<int64_t>(blockIdx.x) * RPB + threadIdx.x / LPR;
+    const bool live = r < N;
+    const float* x = in + (live ? r : 0) * D;
+    const bool in_vec4 = (D % 4 == 0) && ((reinterpret_cast<uintptr_t>(in) & 15) == 0);
+    float mn, mx;
+    row_minmax<LPR, float>(x, live ? D : 0, k, in_vec4, mn, mx);
+    if (!live) return;
+    const __half bias_h = __float2half_rn(mn);
+    const float bias = __half2float(bias_h);
+    const float range = __fsub_rn(mx, bias);
+    float scale = (range == 0.0f) ? 1.0f : __fdiv_rn(range, static_cast<float>(QMAX));
+    __half scale_h = __float2half_rn(scale);
+    scale = __half2float(scale_h);
+    if (scale == 0.0f) {
+        scale = 1.0f;
+        scale_h = __float2half_rn(1.0f);
+    }
+    float inv = __fdiv_rn(1.0f, scale);
+    if (isinf(inv)) {
+        scale_h = __float2half_rn(1.0f);
+        inv = 1.0f;
+    }
+    const int64_t pbytes = (D + PER - 1) / PER;
+    uint8_t* o = out + r * out_stride;
+    uint8_t* codes = TABLE ? o + 4 : o;
+    for (int64_t b = k; b < pbytes; b += LPR) {
+        uint32_t byte = 0;
+#pragma unroll
+        for (int j = 0; j < PER; ++j) {
+            const int64_t c = b * PER + j;
+            if (c < D) {
+                int q = __float2int_rn(__fmul_rn(__fsub_rn(__ldg(x + c), bias), inv));
+                q = max(0, min(QMAX, q));
+                byte |= static_cast<uint32_t>(q) << (j * BITS);
+            }
+        }
+        codes[b] = static_cast<uint8_t>(byte);
+    }
+    if (k == 0) {
+        const uint32_t h = __half_as_ushort(scale_h) | (static_cast<uint32_t>(__half_as_ushort(bias_h)) << 16);
+        uint8_t* hp = TABLE ? o : o + pbytes;
+        hp[0] = h & 0xff; hp[1] = (h >> 8) & 0xff; hp[2] = (h >> 16) & 0xff; hp[3] = (h >> 24) & 0xff;
+    }
+    if (TABLE)
+        for (int64_t c = 4 + pbytes + k; c < out_stride; c += LPR) o[c] = 0;
+}
+
+template <int BITS>
+__global__ void __launch_bounds__(kThreads)
+dequantize_nbit_kernel(const uint8_t* __restrict__ in, int64_t N, int64_t Dq, float* __restrict__ out)
+{
+    constexpr int PER = 8 / BITS;
+    constexpr uint32_t MASK = (1u << BITS) - 1u;
+    const int lane = threadIdx.x & 31;
+    const int64_t r = static_cast<int64_t>(blockIdx.x) * (kThreads / 32) + (threadIdx.x >> 5);
+    if (r >= N) return;
+    const int64_t pbytes = Dq - 4;
+    const int64_t D = pbytes * PER;
+    const uint8_t* q = in + r * Dq;
+    const float scale = half_bits_to_float(__ldg(q + pbytes) | (static_cast<uint32_t>(__ldg(q + pbytes + 1)) << 8));
+    const float bias = half_bits_to_float(__ldg(q + pbytes + 2) | (static_cast<uint32_t>(__ldg(q + pbytes + 3)) << 8));
+    float* o = out + r * D;
+    for (int64_t c = lane; c < D; c += 32) {
+        const uint32_t v = (__ldg(q + c / PER) >> ((c % PER) * BITS)) & MASK;
+        o[c] = fmaf(static_cast<float>(v), scale, bias);
+    }
+}
+
+// ---- packing quantizer output into table rows ----------------------------------
+
+template <int SRC_BITS>
+__global__ void __launch_bounds__(kThreads)
+pack_rows_kernel(const uint8_t* __restrict__ fused, int64_t N, int64_t pbytes, int64_t row_bytes, uint8_t* __restrict__ rows)
+{
+    const int lane = threadIdx.x & 31;
+    const int64_t r = static_cast<int64_t>(blockIdx.x) * (kThreads / 32) + (threadIdx.x >> 5);
+    if (r >= N) return;
+    constexpr int TAIL = SRC_BITS == 8 ? 8 : 4;
+    const uint8_t* f = fused + r * (pbytes + TAIL);
+    uint8_t* o = rows + r * row_bytes;
+    if (lane == 0) {
+        uint32_t h;
+        if (SRC_BITS == 8) {
+            uint32_t sb[2] = {0u, 0u};
+#pragma unroll
+            for (int j = 0; j < 8; ++j) sb[j >> 2] |= static_cast<uint32_t>(__ldg(f + pbytes + j)) << (8 * (j & 3));
+            h = f32_to_f16_bits(__uint_as_float(sb[0])) | (f32_to_f16_bits(__uint_as_float(sb[1])) << 16);
+        } else {
+            h = 0;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) h |= static_cast<uint32_t>(__ldg(f + pbytes + j)) << (8 * j);
+        }
+        o[0] = h & 0xff; o[1] = (h >> 8) & 0xff; o[2] = (h >> 16) & 0xff; o[3] = (h >> 24) & 0xff;
+    }
+    for (int64_t c = lane; c < pbytes; c += 32) o[4 + c] = __ldg(f + c);
+    for (int64_t c = 4 + pbytes + lane; c < row_bytes; c += 32) o[c] = 0;
+}
+
+// fp32 [N, D] -> fp16 table rows (no header), stride row_bytes, padding zeroed.
+__global__ void __launch_bounds__(kThreads)
+cast_fp16_rows_kernel(const float* __restrict__ in, int64_t N, int64_t D, int64_t row_bytes, uint8_t* __restrict__ rows)
+{
+    const int lane = threadIdx.x & 31;
+    const int64_t r = static_cast<int64_t>(blockIdx.x) * (kThreads / 32) + (threadIdx.x >> 5);
+    if (r >= N) return;
+    const float* x = in + r * D;
+    uint8_t* o = rows + r * row_bytes;
+    for (int64_t c = lane; c < D; c += 32) {
+        const uint32_t h = f32_to_f16_bits(__ldg(x + c));
+        o[2 * c] = h & 0xff;
+        o[2 * c + 1] = (h >> 8) & 0xff;
+    }
+    for (int64_t c = 2 * D + lane; c < row_bytes; c += 32) o[c] = 0;
+}
+
+template <typename K, typename... A>
+int launch_rows(K kernel, int lpr, int64_t N, cudaStream_t s, const char* name, A... args)
+{
+    if (N <= 0) return TBE_B200_OK;
+    const int64_t rpb = kThreads / lpr;
+    const int64_t blocks = (N + rpb - 1) / rpb;
+    if (blocks > 0x7fffffffll) return fail(TBE_B200_ERR_UNSUPPORTED, "%s: too many rows for one launch", name);
+    kernel<<<static_cast<unsigned>(blocks), kThreads, 0, s>>>(args...);
+    return check_launch(name);
+}
+
+}  // namespace
+
+// Shared by the two public 8-bit quantizer entry points.
+int quantize_8bit_impl(const void* input, int in_is_half, int64_t N, int64_t D, uint8_t* out, int64_t out_stride,
+                       bool table, cudaStream_t s)
+{
+    const int lpr = (D <= 64) ? 8 : 32;
+#define TBE_Q8(LPR, T, TAB) \
+    return launch_rows(quantize_8bit_kernel<LPR, T, TAB>, LPR, N, s, "quantize_8bit_kernel", static_cast<const T*>(input), N, D, out, out_stride)
+    if (in_is_half) {
+        if (table) { if (lpr == 8) TBE_Q8(8, __half, true); else TBE_Q8(32, __half, true); }
+        else { if (lpr == 8) TBE_Q8(8, __half, false); else TBE_Q8(32, __half, false); }
+    } else {
+        if (table) { if (lpr == 8) TBE_Q8(8, float, true); else TBE_Q8(32, float, true); }
+        else { if (lpr == 8) TBE_Q8(8, float, false); else TBE_Q8(32, float, false); }
+    }
+#undef TBE_Q8
+}
+
+int quantize_nbit_impl(int bit_rate, const float* input, int64_t N, int64_t D, uint8_t* out, int64_t out_stride,
+                       bool table, cudaStream_t s)
+{
+    const int lpr = (D <= 128) ? 8 : 32;
+#define TBE_QN(LPR, BITS, TAB) \
+    return launch_rows(quantize_nbit_kernel<LPR, BITS, TAB>, LPR, N, s, "quantize_nbit_kernel", input, N, D, out, out_stride)
+    if (bit_rate == 4) {
+        if (table) { if (lpr == 8) TBE_QN(8, 4, true); else TBE_QN(32, 4, true); }
+        else { if (lpr == 8) TBE_QN(8, 4, false); else TBE_QN(32, 4, false); }
+    } else {
+        if (table) { if (lpr == 8) TBE_QN(8, 2, true); else TBE_QN(32, 2, true); }
+        else { if (lpr == 8) TBE_QN(8, 2, false); else TBE_QN(32, 2, false); }
+    }
+#undef TBE_QN
+}
+
+}  // namespace tbe
+
+using namespace tbe;
+
+extern "C" int tbe_b200_quantize_8bit_rowwise(const void* input, int32_t in_is_half, int64_t nrows, int64_t ncols,
+                                              uint8_t* output, tbe_b200_stream_t stream)
+{
+    if (nrows < 0 || ncols < 0) return fail(TBE_B200_ERR_INVALID_ARGUMENT, "quantize_8bit_rowwise: negative size");
+    if (nrows > 0 && (!input || !output)) return fail(TBE_B200_ERR_INVALID_ARGUMENT, "quantize_8bit_rowwise: NULL pointer");
+    return quantize_8bit_impl(input, in_is_half, nrows, ncols, output, ncols + 8, false, reinterpret_cast<cudaStream_t>(stream));
+}
+
+extern "C" int tbe_b200_dequantize_8bit_rowwise(const uint8_t* input, int64_t nrows, int64_t ncols_q, void* output,
+                                                int32_t out_is_half, tbe_b200_stream_t stream)
+{
+    if (nrows < 0 || ncols_q < 8)
+        return fail(TBE_B200_ERR_INVALID_ARGUMENT, "dequantize_8bit_rowwise: rows need at least the 8 scale/bias bytes");
+    if (nrows > 0 && (!input || !output)) return fail(TBE_B200_ERR_INVALID_ARGUMENT, "dequantize_8bit_rowwise: NULL pointer");
+    cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+    const int lpr = (ncols_q - 8 <= 64) ? 8 : 32;
+    if (out_is_half) {
+        if (lpr == 8) return launch_rows(dequantize_8bit_kernel<8, __half>, 8, nrows, s, "dequantize_8bit_kernel", input, nrows, ncols_q, static_cast<__half*>(output));
+        return launch_rows(dequantize_8bit_kernel<32, __half>, 32, nrows, s, "dequantize_8bit_kernel", input, nrows, ncols_q, static_cast<__half*>(output));
+    }
+    if (lpr == 8) return launch_rows(dequantize_8bit_kernel<8, float>, 8, nrows, s, "dequantize_8bit_kernel", input, nrows, ncols_q, static_cast<float*>(output));
+    return launch_rows(dequantize_8bit_kernel<32, float>, 32, nrows, s, "dequantize_8bit_kernel", input, nrows, ncols_q, static_cast<float*>(output));
+}
+
+extern "C" int tbe_b200_quantize_nbit_rowwise_sbhalf(int32_t bit_rate, const float* input, int64_t nrows, int64_t ncols,
+                                                     uint8_t* output, tbe_b200_stream_t stream)
+{
+    if (bit_rate != 2 && bit_rate != 4)
+        return fail(TBE_B200_ERR_UNSUPPORTED, "quantize_nbit_rowwise_sbhalf: bit_rate must be 2 or 4, got %d", bit_rate);
+    if (nrows < 0 || ncols < 0) return fail(TBE_B200_ERR_INVALID_ARGUMENT, "quantize_nbit_rowwise_sbhalf: negative size");
+    if (nrows > 0 && (!input || !output)) return fail(TBE_B200_ERR_INVALID_ARGUMENT, "quantize_nbit_rowwise_sbhalf: NULL pointer");
+    const int per = 8 / bit_rate;
+    return quantize_nbit_impl(bit_rate, input, nrows, ncols, output, (ncols + per - 1) / per + 4, false,
+                              reinterpret_cast<cudaStream_t>(stream));
+}
+
+extern "C" int tbe_b200_dequantize_nbit_rowwise_sbhalf(int32_t bit_rate, const uint8_t* input, int64_t nrows,
+                                                       int64_t ncols_q, float* output, tbe_b200_stream_t stream)
+{
+    if (bit_rate != 2 && bit_rate != 4)
+        return fail(TBE_B200_ERR_UNSUPPORTED, "dequantize_nbit_rowwise_sbhalf: bit_rate must be 2 or 4, got %d", bit_rate);
+    if (nrows < 0 || ncols_q < 4)
+        return fail(TBE_B200_ERR_INVALID_ARGUMENT, "dequantize_nbit_rowwise_sbhalf: rows need at least the 4 scale/bias bytes");
+    if (nrows > 0 && (!input || !output)) return fail(TBE_B200_ERR_INVALID_ARGUMENT, "dequantize_nbit_rowwise_sbhalf: NULL pointer");
+    cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+    if (bit_rate == 4) return launch_rows(dequantize_nbit_kernel<4>, 32, nrows, s, "dequantize_nbit_kernel", input, nrows, ncols_q, output);
+    return launch_rows(dequantize_nbit_kernel<2>, 32, nrows, s, "dequantize_nbit_kernel", input, nrows, ncols_q, output);
+}
+
+extern "C" int tbe_b200_pack_table_rows(int32_t src_bits, const uint8_t* fused, int64_t nrows, int64_t ncols,
+                                        int64_t row_bytes, uint8_t* rows, tbe_b200_stream_t stream)
+{
+    if (src_bits != 8 && src_bits != 4 && src_bits != 2)
+        return fail(TBE_B200_ERR_UNSUPPORTED, "pack_table_rows: src_bits must be 8, 4 or 2, got %d", src_bits);
+    if (nrows < 0 || ncols < 0) return fail(TBE_B200_ERR_INVALID_ARGUMENT, "pack_table_rows: negative size");
+    const int per = 8 / src_bits;
+    const int64_t pbytes = (ncols + per - 1) / per;
+    if (row_bytes < pbytes + 4) return fail(TBE_B200_ERR_INVALID_ARGUMENT, "pack_table_rows: row_bytes %lld too small for %lld payload bytes + header",
+                                            (long long)row_bytes, (long long)pbytes);
+    if (nrows > 0 && (!fused || !rows)) return fail(TBE_B200_ERR_INVALID_ARGUMENT, "pack_table_rows: NULL pointer");
+    cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+    if (src_bits == 8) return launch_rows(pack_rows_kernel<8>, 32, nrows, s, "pack_rows_kernel", fused, nrows, pbytes, row_bytes, rows);
+    return launch_rows(pack_rows_kernel<4>, 32, nrows, s, "pack_rows_kernel", fused, nrows, pbytes, row_bytes, rows);
+}
+
+extern "C" int tbe_b200_quantize_to_table_rows(int32_t weight_ty, const float* input, int64_t nrows, int64_t ncols,
+                                               int64_t row_bytes, uint8_t* rows, tbe_b200_stream_t stream)
+{
+    if (nrows < 0 || ncols < 0) return fail(TBE_B200_ERR_INVALID_ARGUMENT, "quantize_to_table_rows: negative size");
+    if (nrows > 0 && (!input || !rows)) return fail(TBE_B200_ERR_INVALID_ARGUMENT, "quantize_to_table_rows: NULL pointer");
+    cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+    int64_t need;
+    switch (weight_ty) {
+        case TBE_B200_INT8: need = ncols + 4; break;
+        case TBE_B200_INT4: need = (ncols + 1) / 2 + 4; break;
+        case TBE_B200_INT2: need = (ncols + 3) / 4 + 4; break;
+        case TBE_B200_FP16: need = 2 * ncols; break;
+        default:
+            return fail(TBE_B200_ERR_UNSUPPORTED, "quantize_to_table_rows: weight type %d (supported: FP16, INT8, INT4, INT2)", weight_ty);
+    }
+    if (row_bytes < need)
+        return fail(TBE_B200_ERR_INVALID_ARGUMENT, "quantize_to_table_rows: row_bytes %lld smaller than the %lld bytes a row needs",
+                    (long long)row_bytes, (long long)need);
+    if (weight_ty == TBE_B200_INT8) return quantize_8bit_impl(input, 0, nrows, ncols, rows, row_bytes, true, s);
+    if (weight_ty == TBE_B200_INT4) return quantize_nbit_impl(4, input, nrows, ncols, rows, row_bytes, true, s);
+    if (weight_ty == TBE_B200_INT2) return quantize_nbit_impl(2, input, nrows, ncols, rows, row_bytes, true, s);
+    return launch_rows(cast_fp16_rows_kernel, 32, nrows, s, "cast_fp16_rows_kernel", input, nrows, ncols, row_bytes, rows);
+}

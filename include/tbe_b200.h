@@ -1,0 +1,175 @@
+/*
+ * tbe_b200 -- C ABI of the B200 (sm_100a) quantized table-batched-embedding
+ * inference library (libtbe_b200.so).
+ *
+ * This is the boundary a host framework binds to.  It plays the role that the
+ * per-operator C entry points of libcust_opapi.so play in the reference
+ * (aclnn<Op>GetWorkspaceSize + aclnn<Op>, looked up and called by EXEC_NPU_CMD,
+ * src/common/pytorch_npu_helper.hpp:536-585): plain pointers and sizes in, an int
+ * status out, work enqueued asynchronously on the stream the caller names.
+ *
+ * Conventions
+ *   - Every pointer is a DEVICE pointer on the current CUDA device unless the
+ *     comment says "host".  The library never allocates, frees or synchronises.
+ *   - Every call returns TBE_B200_OK (0) or a negative tbe_b200_status; the
+ *     message of the last failure on the calling thread is tbe_b200_last_error().
+ *   - Calls are re-entrant and may be issued from any thread.
+ *   - `stream` is a cudaStream_t (0 = the default stream).
+ */
+#ifndef TBE_B200_H_
+#define TBE_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct CUstream_st* tbe_b200_stream_t;
+
+typedef enum {
+    TBE_B200_OK = 0,
+    TBE_B200_ERR_INVALID_ARGUMENT = -1,
+    TBE_B200_ERR_UNSUPPORTED = -2,
+    TBE_B200_ERR_CUDA = -3
+} tbe_b200_status;
+
+/* Weight / output element types: SparseType of
+ * int_nbit_split_embedding_codegen_lookup_function.cpp:24-33. */
+typedef enum {
+    TBE_B200_FP32 = 0,
+    TBE_B200_FP16 = 1,
+    TBE_B200_INT8 = 2,
+    TBE_B200_INT4 = 3,
+    TBE_B200_INT2 = 4,
+    TBE_B200_BF16 = 5,
+    TBE_B200_FP8 = 6
+} tbe_b200_sparse_type;
+
+/* PoolingMode of int_nbit_split_embedding_codegen_lookup_function.cpp:18-22. */
+typedef enum { TBE_B200_POOL_SUM = 0, TBE_B200_POOL_MEAN = 1, TBE_B200_POOL_NONE = 2 } tbe_b200_pooling_mode;
+
+/*
+ * Arguments of the pooled / sequence lookup.  Replaces the argument list that
+ * int_nbit_split_embedding_codegen_lookup_function_npu hands to
+ * aclnnIntNbitSplitEmbeddingCodegenLookupFunction
+ * (int_nbit_split_embedding_codegen_lookup_function.cpp:139-165) together with the
+ * tiling data the host computes for it
+ * (c310/op_host/int_nbit_split_embedding_codegen_lookup_function_tiling.h:20-43).
+ *
+ * Geometry: T tables, B bags per table; bag i = t*B + b owns
+ * indices[offsets[i] .. offsets[i+1]); table t starts at byte weights_offsets[t]
+ * of dev_weights; a row of table t is
+ *   [fp16 scale][fp16 bias][payload]   for INT8 / INT4 / INT2
+ *   [payload]                          for FP32 / FP16 / FP8
+ * padded to a multiple of row_alignment bytes; D_t = D_offsets[t+1]-D_offsets[t].
+ *
+ * Pooled modes write bag (t, b) to
+ *   dst(b) + (b % rows_per_dest) * output_stride + col(t)
+ * where col(t) = output_col_offsets ? output_col_offsets[t] : D_offsets[t] and
+ * dst(b) = dest_outputs ? dest_outputs[b / rows_per_dest] : output (in which
+ * case rows_per_dest is ignored and b is used as is).  The two optional fields
+ * let one launch pool, scatter the batch over several destination buffers
+ * (peer GPUs' memory included) and place each table at its final, permuted
+ * column in one pass; leave them NULL for the plain operator.
+ * An empty bag writes zeros.  Index -1 contributes nothing but counts in MEAN.
+ *
+ * Pooling NONE writes row n of `indices` to output + n*output_stride, D_t
+ * elements wide.
+ */
+typedef struct {
+    const uint8_t* dev_weights;         /* all tables, flat bytes */
+    int64_t dev_weights_bytes;          /* size of dev_weights (checked against nothing on device; 0 = unknown) */
+    const int64_t* weights_offsets;     /* [T] byte offset of each table */
+    const uint8_t* weights_tys;         /* [T] tbe_b200_sparse_type per table */
+    const int32_t* D_offsets;           /* [T+1] prefix sum of the tables' D */
+    int32_t T;
+    int64_t B;
+    int64_t total_D;                    /* D_offsets[T] */
+    int32_t max_D;                      /* max over tables of D_t (host-known; sizes the launch) */
+    const void* indices;                /* [N] int32 or int64 */
+    const void* offsets;                /* [T*B+1], same width as indices */
+    int32_t index_bits;                 /* 32 or 64 */
+    int64_t num_indices;                /* N */
+    const float* indice_weights;        /* [N] per-sample weights, or NULL */
+    int32_t pooling_mode;               /* tbe_b200_pooling_mode */
+    int32_t output_dtype;               /* TBE_B200_FP32 / FP16 / BF16 */
+    int32_t row_alignment;              /* bytes; the operator's default is 16 */
+    int32_t fp8_exponent_bits;          /* FP8 tables only */
+    int32_t fp8_exponent_bias;          /* FP8 tables only */
+    void* output;                       /* [B, output_stride] (pooled) or [N, output_stride] (NONE) */
+    int64_t output_stride;              /* elements between consecutive output rows */
+    const int64_t* output_col_offsets;  /* [T] or NULL (pooled modes) */
+    void* const* dest_outputs;          /* [ceil(B / rows_per_dest)] device array of base pointers, or NULL */
+    int64_t rows_per_dest;              /* used only with dest_outputs */
+    int32_t* error_flag;                /* optional device word: or'ed with 1 when an index < -1 is met
+                                           (that row is skipped); NULL = no reporting */
+} tbe_b200_lookup_args;
+
+/* Pooled (SUM / MEAN) or sequence (NONE) lookup over fused INT8 / INT4 / INT2 /
+ * FP16 / FP32 / FP8 rows; fp32 accumulation; output cast round-to-nearest-even.
+ * Replaces aclnnIntNbitSplitEmbeddingCodegenLookupFunction
+ * (c310/op_kernel/int_nbit_split_embedding_codegen_lookup_function.cpp:58-89). */
+int tbe_b200_int_nbit_lookup(const tbe_b200_lookup_args* args, tbe_b200_stream_t stream);
+
+/* FloatToFused8BitRowwiseQuantized: fp32 (or fp16 when in_is_half) [nrows, ncols]
+ * -> uint8 [nrows, ncols + 8]: codes, fp32 scale, fp32 bias.  Upstream fbgemm op
+ * that the reference inherits through `import fbgemm_gpu`
+ * (fbgemm_ascend/__init__.py:9). */
+int tbe_b200_quantize_8bit_rowwise(const void* input, int32_t in_is_half, int64_t nrows, int64_t ncols,
+                                   uint8_t* output, tbe_b200_stream_t stream);
+
+/* Fused8BitRowwiseQuantizedToFloat (or ...ToHalf when out_is_half):
+ * uint8 [nrows, ncols_q] -> [nrows, ncols_q - 8]. */
+int tbe_b200_dequantize_8bit_rowwise(const uint8_t* input, int64_t nrows, int64_t ncols_q, void* output,
+                                     int32_t out_is_half, tbe_b200_stream_t stream);
+
+/* FloatToFusedNBitRowwiseQuantizedSBHalf, bit_rate 2 or 4: fp32 [nrows, ncols] ->
+ * uint8 [nrows, ncols*bit_rate/8 + 4]: packed codes, fp16 scale, fp16 bias. */
+int tbe_b200_quantize_nbit_rowwise_sbhalf(int32_t bit_rate, const float* input, int64_t nrows, int64_t ncols,
+                                          uint8_t* output, tbe_b200_stream_t stream);
+
+/* FusedNBitRowwiseQuantizedSBHalfToFloat: inverse of the above. */
+int tbe_b200_dequantize_nbit_rowwise_sbhalf(int32_t bit_rate, const uint8_t* input, int64_t nrows,
+                                            int64_t ncols_q, float* output, tbe_b200_stream_t stream);
+
+/* Turn quantizer output rows into table rows: move the scale/bias pair to the
+ * front as fp16 (8-bit rows: fp32 -> fp16 round-to-nearest-even; n-bit rows:
+ * already fp16) and pad each row to row_bytes.  src_bits 8, 4 or 2.  This is the
+ * layout step the upstream inference module performs when weights are assigned
+ * (exercised by the reference through split_embedding_weights(),
+ * test_int_nbit_split_embedding_codegen_lookup_function.py:144-156). */
+int tbe_b200_pack_table_rows(int32_t src_bits, const uint8_t* fused, int64_t nrows, int64_t ncols,
+                             int64_t row_bytes, uint8_t* rows, tbe_b200_stream_t stream);
+
+/* Quantize fp32 [nrows, ncols] straight into table rows of weight type
+ * weight_ty (INT8, INT4, INT2: quantizer + header-first packing in one pass, same
+ * bytes as the quantizer followed by tbe_b200_pack_table_rows; FP16: a
+ * round-to-nearest-even cast), row stride row_bytes, padding zeroed.  For building
+ * tables too large to hold the intermediate quantizer output. */
+int tbe_b200_quantize_to_table_rows(int32_t weight_ty, const float* input, int64_t nrows, int64_t ncols,
+                                    int64_t row_bytes, uint8_t* rows, tbe_b200_stream_t stream);
+
+/* permute_pooled_embs: out[:, inv_offset_dim_list[i] .. inv_offset_dim_list[i+1]) =
+ * in[:, offset_dim_list[p] .. offset_dim_list[p+1]), p = permute_list[i].
+ * Replaces aclnnPermutePooledEmbs (permute_pooled_embs.cpp:100-101; kernel
+ * v220/op_kernel/permute_pooled_embs_kernel.h:173-211).  elem_bytes 2 or 4.
+ * in_stride / out_stride: elements between consecutive rows.  A permute entry
+ * outside [0, T) copies nothing for that feature and sets *error_flag (if given). */
+int tbe_b200_permute_pooled_embs(const void* pooled_embs, int64_t B, int64_t total_D, int32_t elem_bytes,
+                                 int64_t in_stride, int64_t out_stride, const int64_t* offset_dim_list,
+                                 const int64_t* permute_list, const int64_t* inv_offset_dim_list, int32_t T,
+                                 void* output, int32_t* error_flag, tbe_b200_stream_t stream);
+
+/* Message of the last failure on the calling thread ("" if none).  Host pointer,
+ * valid until the next failing call on the same thread. */
+const char* tbe_b200_last_error(void);
+
+/* Library version, major*10000 + minor*100 + patch. */
+int tbe_b200_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* TBE_B200_H_ */
