@@ -25,6 +25,7 @@
 //     take a byte-wise path with the same results.
 #include <stdarg.h>
 #include <stdio.h>
+#include <stdlib.h>
 
 #include "tbe_common.cuh"
 
@@ -113,17 +114,69 @@ __device__ __forceinline__ void store_out(void* seg, int e0, const float* v, int
 
 // ---- per-type row access ---------------------------------------------------
 //
-// Every lane owns 16 accumulator "slots".  A path says which bytes a lane loads
-// for a row (load), how they add into the slots (accum), and which element of
-// the row a slot stands for (elem).  `unit` is the lane's position among the
-// 16-slot units of the row: unit = block * LPR + k.
+// Every lane owns 16 accumulator "slots".  A path says which bytes a lane fetches
+// for a row (issue), how the fetched bytes add into the slots (accum), and which
+// element of the row a slot stands for (elem).  `unit` is the lane's position
+// among the 16-slot units of the row: unit = block * LPR + k.
+//
+// Rows are fetched with cp.async straight into shared memory, never through
+// registers: each lane has private staging slots (one per pass of a chunk, two
+// chunks deep), so the rows of two chunks are in flight per warp while the
+// accumulators and addresses are all the registers a lane needs.  A lane reads
+// back only what it fetched itself, so no warp barrier is involved.
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+
+// 16-byte asynchronous copy global -> shared, L2 only; `bytes` = 16, or 0 to write zeros without reading.
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, int bytes)
+{
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async8(uint32_t dst, const void* src, int bytes)
+{
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 8, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async4(uint32_t dst, const void* src, int bytes)
+{
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+__device__ __forceinline__ uint4 lds16(uint32_t a)
+{
+    uint4 v;
+    asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ uint2 lds8(uint32_t a)
+{
+    uint2 v;
+    asm volatile("ld.shared.v2.b32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ uint32_t lds4(uint32_t a)
+{
+    uint32_t v;
+    asm volatile("ld.shared.b32 %0, [%1];" : "=r"(v) : "r"(a));
+    return v;
+}
+
+// Staging memory of one warp: two chunk buffers of kChunkBytes (a lane's slot for pass u is at
+// (u*32 + lane) * slot_bytes) and, for header types, one 4-byte side slot per (buffer, pass, group).
+constexpr int kChunkBytes = 2048;
+constexpr int kMaxPasses = 8;
+constexpr int kSideBytes = 2 * kMaxPasses * 16 * 4;
+constexpr int kWarpSmemBytes = 2 * kChunkBytes + kSideBytes;
 
 struct LaneCtx {
     int unit;        // 16-slot unit handled by this lane in the current block
     int D;           // elements per row
+    int k;           // lane index within its row group
     bool active;     // this unit exists in the row
     bool wrap;       // INT8/INT4 header lane that also takes the row's tail
-    bool first_blk;  // block 0: the header chunk is held by lane k == 0 of the group
+    bool first_blk;  // block 0: the header is the first word of unit 0
     uint32_t fp8_shift;
     float fp8_mult;
 };
@@ -133,33 +186,35 @@ struct Path;
 
 template <>
 struct Path<TBE_B200_INT8> {
-    struct Regs {
-        uint4 v;
-        uint32_t hdr;
-    };
     static constexpr bool kHasHeader = true;
+    static constexpr int kSlotBytes = 16;
+    static constexpr int kPasses = 4;   // passes per chunk (x 32 lanes x 16 B = 2 KB)
     // 16-byte chunks of the row: chunk c covers elements [16c - 4, 16c + 12).
     static __device__ __forceinline__ int units(int D, bool wrap) { return wrap ? D / 16 : (D + 4 + 15) / 16; }
     static __device__ __forceinline__ bool can_wrap(int D) { return (D & 15) == 0; }
-    static __device__ __forceinline__ void load(Regs& r, const uint8_t* row, const LaneCtx& cx, bool ok)
+    // The side slot of the header lane gets the row's tail (elements D-4 .. D-1) when the row
+    // wraps, and the header itself in the later blocks of a wide row.
+    template <int LPR>
+    static __device__ __forceinline__ void issue(uint32_t slot, uint32_t side, const uint8_t* row, const uint8_t* safe,
+                                                 const LaneCtx& cx, bool ok)
     {
-        r.v = make_uint4(0u, 0u, 0u, 0u);
-        r.hdr = 0u;
-        if (ok && cx.active) r.v = ldg16(row + cx.unit * 16);
-        if (ok && cx.wrap) r.hdr = ldg4(row + cx.D);            // tail: elements D-4 .. D-1
-        else if (ok && !cx.first_blk) r.hdr = ldg4(row);        // later blocks fetch the header directly
+        if (cx.active) cp_async16(slot, ok ? row + cx.unit * 16 : safe, ok ? 16 : 0);
+        if (cx.k == 0 && (cx.wrap || !cx.first_blk)) cp_async4(side, ok ? row + (cx.wrap ? cx.D : 0) : safe, ok ? 4 : 0);
     }
     template <int LPR>
-    static __device__ __forceinline__ void accum(Regs& r, const LaneCtx& cx, float w, float (&acc)[16], float& bias_acc)
+    static __device__ __forceinline__ void accum(uint32_t slot, uint32_t side, const LaneCtx& cx, float w, float (&acc)[16],
+                                                 float& bias_acc)
     {
-        uint32_t hdr = r.hdr;
-        if (cx.first_blk) {
-            hdr = __shfl_sync(kFull, r.v.x, 0, LPR);
-            if (cx.wrap) r.v.x = r.hdr;
+        uint4 v = cx.active ? lds16(slot) : make_uint4(0u, 0u, 0u, 0u);
+        uint32_t hdr = v.x;
+        if (cx.k == 0 && (cx.wrap || !cx.first_blk)) {
+            const uint32_t s = lds4(side);
+            if (cx.wrap) v.x = s; else hdr = s;
         }
+        hdr = __shfl_sync(kFull, hdr, 0, LPR);
         const float s = half_bits_to_float(hdr & 0xffffu) * w;
         bias_acc = fmaf(half_bits_to_float(hdr >> 16), w, bias_acc);
-        const uint32_t words[4] = {r.v.x, r.v.y, r.v.z, r.v.w};
+        const uint32_t words[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
 #pragma unroll
@@ -169,7 +224,8 @@ struct Path<TBE_B200_INT8> {
             }
         }
     }
-    static __device__ __forceinline__ int elem(const LaneCtx& cx, int slot, int /*LPR*/)
+    template <int LPR>
+    static __device__ __forceinline__ int elem(const LaneCtx& cx, int slot)
     {
         if (cx.wrap && slot < 4) return cx.D - 4 + slot;
         return 16 * cx.unit - 4 + slot;
@@ -178,33 +234,33 @@ struct Path<TBE_B200_INT8> {
 
 template <>
 struct Path<TBE_B200_INT4> {
-    struct Regs {
-        uint2 v;
-        uint32_t hdr;
-    };
     static constexpr bool kHasHeader = true;
+    static constexpr int kSlotBytes = 8;
+    static constexpr int kPasses = 8;   // x 32 lanes x 8 B = 2 KB
     // 8-byte chunks: chunk c covers elements [16c - 8, 16c + 8).
     static __device__ __forceinline__ int units(int D, bool wrap) { return wrap ? D / 16 : (D / 2 + 4 + 7) / 8; }
     static __device__ __forceinline__ bool can_wrap(int D) { return (D & 15) == 0; }
-    static __device__ __forceinline__ void load(Regs& r, const uint8_t* row, const LaneCtx& cx, bool ok)
+    template <int LPR>
+    static __device__ __forceinline__ void issue(uint32_t slot, uint32_t side, const uint8_t* row, const uint8_t* safe,
+                                                 const LaneCtx& cx, bool ok)
     {
-        r.v = make_uint2(0u, 0u);
-        r.hdr = 0u;
-        if (ok && cx.active) r.v = ldg8(row + cx.unit * 8);
-        if (ok && cx.wrap) r.hdr = ldg4(row + cx.D / 2);        // tail: elements D-8 .. D-1
-        else if (ok && !cx.first_blk) r.hdr = ldg4(row);
+        if (cx.active) cp_async8(slot, ok ? row + cx.unit * 8 : safe, ok ? 8 : 0);
+        if (cx.k == 0 && (cx.wrap || !cx.first_blk)) cp_async4(side, ok ? row + (cx.wrap ? cx.D / 2 : 0) : safe, ok ? 4 : 0);
     }
     template <int LPR>
-    static __device__ __forceinline__ void accum(Regs& r, const LaneCtx& cx, float w, float (&acc)[16], float& bias_acc)
+    static __device__ __forceinline__ void accum(uint32_t slot, uint32_t side, const LaneCtx& cx, float w, float (&acc)[16],
+                                                 float& bias_acc)
     {
-        uint32_t hdr = r.hdr;
-        if (cx.first_blk) {
-            hdr = __shfl_sync(kFull, r.v.x, 0, LPR);
-            if (cx.wrap) r.v.x = r.hdr;
+        uint2 v = cx.active ? lds8(slot) : make_uint2(0u, 0u);
+        uint32_t hdr = v.x;
+        if (cx.k == 0 && (cx.wrap || !cx.first_blk)) {
+            const uint32_t s = lds4(side);
+            if (cx.wrap) v.x = s; else hdr = s;
         }
+        hdr = __shfl_sync(kFull, hdr, 0, LPR);
         const float s = half_bits_to_float(hdr & 0xffffu) * w;
         bias_acc = fmaf(half_bits_to_float(hdr >> 16), w, bias_acc);
-        const uint32_t words[2] = {r.v.x, r.v.y};
+        const uint32_t words[2] = {v.x, v.y};
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
 #pragma unroll
@@ -214,7 +270,8 @@ struct Path<TBE_B200_INT4> {
             }
         }
     }
-    static __device__ __forceinline__ int elem(const LaneCtx& cx, int slot, int /*LPR*/)
+    template <int LPR>
+    static __device__ __forceinline__ int elem(const LaneCtx& cx, int slot)
     {
         if (cx.wrap && slot < 8) return cx.D - 8 + slot;
         return 16 * cx.unit - 8 + slot;
@@ -223,23 +280,24 @@ struct Path<TBE_B200_INT4> {
 
 template <>
 struct Path<TBE_B200_FP8> {
-    struct Regs {
-        uint4 v;
-    };
     static constexpr bool kHasHeader = false;
+    static constexpr int kSlotBytes = 16;
+    static constexpr int kPasses = 4;
     static __device__ __forceinline__ int units(int D, bool) { return (D + 15) / 16; }
     static __device__ __forceinline__ bool can_wrap(int) { return false; }
-    static __device__ __forceinline__ void load(Regs& r, const uint8_t* row, const LaneCtx& cx, bool ok)
+    template <int LPR>
+    static __device__ __forceinline__ void issue(uint32_t slot, uint32_t, const uint8_t* row, const uint8_t* safe,
+                                                 const LaneCtx& cx, bool ok)
     {
-        r.v = make_uint4(0u, 0u, 0u, 0u);
-        if (ok && cx.active) r.v = ldg16(row + cx.unit * 16);
+        if (cx.active) cp_async16(slot, ok ? row + cx.unit * 16 : safe, ok ? 16 : 0);
     }
     // Byte -> fp32 by bit placement: ((b & 0x7f) << (16 + ebits)) as a float, times
     // 2^(127 - bias), sign bit or'ed in (reference: c310/op_kernel/common.h:120-167).
     template <int LPR>
-    static __device__ __forceinline__ void accum(Regs& r, const LaneCtx& cx, float w, float (&acc)[16], float&)
+    static __device__ __forceinline__ void accum(uint32_t slot, uint32_t, const LaneCtx& cx, float w, float (&acc)[16], float&)
     {
-        const uint32_t words[4] = {r.v.x, r.v.y, r.v.z, r.v.w};
+        const uint4 v = cx.active ? lds16(slot) : make_uint4(0u, 0u, 0u, 0u);
+        const uint32_t words[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
 #pragma unroll
@@ -251,35 +309,37 @@ struct Path<TBE_B200_FP8> {
             }
         }
     }
-    static __device__ __forceinline__ int elem(const LaneCtx& cx, int slot, int) { return 16 * cx.unit + slot; }
+    template <int LPR>
+    static __device__ __forceinline__ int elem(const LaneCtx& cx, int slot) { return 16 * cx.unit + slot; }
 };
 
 template <>
 struct Path<TBE_B200_FP16> {
-    struct Regs {
-        uint4 a, b;
-    };
     static constexpr bool kHasHeader = false;
-    // A unit is two 16-byte chunks LPR chunks apart, so that one load instruction of
-    // a group covers LPR*16 contiguous bytes: with blk = unit / LPR and k = unit % LPR,
-    // chunk_a = 2*blk*LPR + k, chunk_b = chunk_a + LPR; a chunk is 8 elements.
+    static constexpr int kSlotBytes = 32;
+    static constexpr int kPasses = 2;
+    // A unit is two 16-byte chunks LPR chunks apart, so that one copy instruction of a group covers
+    // LPR*16 contiguous bytes: with blk = unit / LPR and k = unit % LPR, chunk_a = 2*blk*LPR + k,
+    // chunk_b = chunk_a + LPR; a chunk is 8 elements.  Bounds are checked per chunk.
     static __device__ __forceinline__ int units(int D, bool) { return (D + 15) / 16; }
     static __device__ __forceinline__ bool can_wrap(int) { return false; }
     template <int LPR>
     static __device__ __forceinline__ int chunk_a(int unit) { return 2 * (unit / LPR) * LPR + (unit % LPR); }
     template <int LPR>
-    static __device__ __forceinline__ void load_l(Regs& r, const uint8_t* row, const LaneCtx& cx, bool ok)
+    static __device__ __forceinline__ void issue(uint32_t slot, uint32_t, const uint8_t* row, const uint8_t* safe,
+                                                 const LaneCtx& cx, bool ok)
     {
-        r.a = make_uint4(0u, 0u, 0u, 0u);
-        r.b = make_uint4(0u, 0u, 0u, 0u);
         const int ca = chunk_a<LPR>(cx.unit);
-        if (ok && cx.active && ca * 8 < cx.D) r.a = ldg16(row + ca * 16);
-        if (ok && cx.active && (ca + LPR) * 8 < cx.D) r.b = ldg16(row + (ca + LPR) * 16);
+        if (ca * 8 < cx.D) cp_async16(slot, ok ? row + ca * 16 : safe, ok ? 16 : 0);
+        if ((ca + LPR) * 8 < cx.D) cp_async16(slot + 16, ok ? row + (ca + LPR) * 16 : safe, ok ? 16 : 0);
     }
     template <int LPR>
-    static __device__ __forceinline__ void accum(Regs& r, const LaneCtx&, float w, float (&acc)[16], float&)
+    static __device__ __forceinline__ void accum(uint32_t slot, uint32_t, const LaneCtx& cx, float w, float (&acc)[16], float&)
     {
-        const uint32_t words[8] = {r.a.x, r.a.y, r.a.z, r.a.w, r.b.x, r.b.y, r.b.z, r.b.w};
+        const int ca = chunk_a<LPR>(cx.unit);
+        const uint4 a = (ca * 8 < cx.D) ? lds16(slot) : make_uint4(0u, 0u, 0u, 0u);
+        const uint4 b = ((ca + LPR) * 8 < cx.D) ? lds16(slot + 16) : make_uint4(0u, 0u, 0u, 0u);
+        const uint32_t words[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
             acc[2 * i] = fmaf(w, half_bits_to_float(words[i] & 0xffffu), acc[2 * i]);
@@ -287,7 +347,7 @@ struct Path<TBE_B200_FP16> {
         }
     }
     template <int LPR>
-    static __device__ __forceinline__ int elem_l(const LaneCtx& cx, int slot)
+    static __device__ __forceinline__ int elem(const LaneCtx& cx, int slot)
     {
         const int ca = chunk_a<LPR>(cx.unit);
         return slot < 8 ? 8 * ca + slot : 8 * (ca + LPR) + slot - 8;
@@ -296,56 +356,42 @@ struct Path<TBE_B200_FP16> {
 
 template <>
 struct Path<TBE_B200_FP32> {
-    struct Regs {
-        uint4 v[4];
-    };
     static constexpr bool kHasHeader = false;
+    static constexpr int kSlotBytes = 64;
+    static constexpr int kPasses = 1;
     // A unit is four 16-byte chunks, LPR chunks apart: chunk_m = 4*blk*LPR + m*LPR + k.
     static __device__ __forceinline__ int units(int D, bool) { return (D + 15) / 16; }
     static __device__ __forceinline__ bool can_wrap(int) { return false; }
     template <int LPR>
     static __device__ __forceinline__ int chunk0(int unit) { return 4 * (unit / LPR) * LPR + (unit % LPR); }
     template <int LPR>
-    static __device__ __forceinline__ void load_l(Regs& r, const uint8_t* row, const LaneCtx& cx, bool ok)
+    static __device__ __forceinline__ void issue(uint32_t slot, uint32_t, const uint8_t* row, const uint8_t* safe,
+                                                 const LaneCtx& cx, bool ok)
+    {
+        const int c0 = chunk0<LPR>(cx.unit);
+#pragma unroll
+        for (int m = 0; m < 4; ++m)
+            if ((c0 + m * LPR) * 4 < cx.D) cp_async16(slot + 16 * m, ok ? row + (c0 + m * LPR) * 16 : safe, ok ? 16 : 0);
+    }
+    template <int LPR>
+    static __device__ __forceinline__ void accum(uint32_t slot, uint32_t, const LaneCtx& cx, float w, float (&acc)[16], float&)
     {
         const int c0 = chunk0<LPR>(cx.unit);
 #pragma unroll
         for (int m = 0; m < 4; ++m) {
-            r.v[m] = make_uint4(0u, 0u, 0u, 0u);
-            if (ok && cx.active && (c0 + m * LPR) * 4 < cx.D) r.v[m] = ldg16(row + (c0 + m * LPR) * 16);
+            const uint4 v = ((c0 + m * LPR) * 4 < cx.D) ? lds16(slot + 16 * m) : make_uint4(0u, 0u, 0u, 0u);
+            acc[4 * m + 0] = fmaf(w, __uint_as_float(v.x), acc[4 * m + 0]);
+            acc[4 * m + 1] = fmaf(w, __uint_as_float(v.y), acc[4 * m + 1]);
+            acc[4 * m + 2] = fmaf(w, __uint_as_float(v.z), acc[4 * m + 2]);
+            acc[4 * m + 3] = fmaf(w, __uint_as_float(v.w), acc[4 * m + 3]);
         }
     }
     template <int LPR>
-    static __device__ __forceinline__ void accum(Regs& r, const LaneCtx&, float w, float (&acc)[16], float&)
-    {
-#pragma unroll
-        for (int m = 0; m < 4; ++m) {
-            acc[4 * m + 0] = fmaf(w, __uint_as_float(r.v[m].x), acc[4 * m + 0]);
-            acc[4 * m + 1] = fmaf(w, __uint_as_float(r.v[m].y), acc[4 * m + 1]);
-            acc[4 * m + 2] = fmaf(w, __uint_as_float(r.v[m].z), acc[4 * m + 2]);
-            acc[4 * m + 3] = fmaf(w, __uint_as_float(r.v[m].w), acc[4 * m + 3]);
-        }
-    }
-    template <int LPR>
-    static __device__ __forceinline__ int elem_l(const LaneCtx& cx, int slot)
+    static __device__ __forceinline__ int elem(const LaneCtx& cx, int slot)
     {
         return 4 * (chunk0<LPR>(cx.unit) + (slot >> 2) * LPR) + (slot & 3);
     }
 };
-
-template <int TY, int LPR>
-__device__ __forceinline__ void path_load(typename Path<TY>::Regs& r, const uint8_t* row, const LaneCtx& cx, bool ok)
-{
-    if constexpr (TY == TBE_B200_FP16 || TY == TBE_B200_FP32) Path<TY>::template load_l<LPR>(r, row, cx, ok);
-    else Path<TY>::load(r, row, cx, ok);
-}
-
-template <int TY, int LPR>
-__device__ __forceinline__ int path_elem(const LaneCtx& cx, int slot)
-{
-    if constexpr (TY == TBE_B200_FP16 || TY == TBE_B200_FP32) return Path<TY>::template elem_l<LPR>(cx, slot);
-    else return Path<TY>::elem(cx, slot, LPR);
-}
 
 // One halving step of the cross-group reduce-scatter: lanes `dist` apart swap the
 // half of their N live values that the other one keeps.
@@ -371,25 +417,65 @@ struct BagInfo {
     bool seg_aligned;       // seg is 16-byte aligned
 };
 
+// The first (up to) 32 indices and weights of a bag, one per lane, fetched ahead of time.
+struct BagHead {
+    int64_t idx;   // -1 beyond the bag
+    float w;
+};
+
+template <typename IdxT>
+__device__ __forceinline__ BagHead load_batch(const IdxT* indices, const float* pw, int n, int lane, int32_t* error_flag)
+{
+    BagHead h;
+    h.idx = -1;
+    h.w = 1.0f;
+    (void)error_flag;
+    if (lane < n) {
+        h.idx = static_cast<int64_t>(ld_stream(indices + lane));
+        if (pw) h.w = ld_stream(pw + lane);
+    }
+    return h;
+}
+
+template <typename IdxT>
+__device__ __forceinline__ int64_t shfl_idx(int64_t v, int src)
+{
+    if constexpr (sizeof(IdxT) == 8) {
+        const uint32_t lo = __shfl_sync(kFull, static_cast<uint32_t>(v), src);
+        const uint32_t hi = __shfl_sync(kFull, static_cast<uint32_t>(static_cast<uint64_t>(v) >> 32), src);
+        return static_cast<int64_t>((static_cast<uint64_t>(hi) << 32) | lo);
+    } else {
+        return static_cast<int64_t>(__shfl_sync(kFull, static_cast<int32_t>(v), src));
+    }
+}
+
 // Pools one bag whose rows are 16-byte aligned with a 16-byte-multiple stride.
+// `head` holds the bag's first 32 indices/weights; `wsm` is the warp's staging memory.
 template <int TY, int LPR, typename IdxT>
-__device__ __forceinline__ void pool_bag(const LookupParams& p, const BagInfo& bag, int lane)
+__device__ __forceinline__ void pool_bag(const LookupParams& p, const BagInfo& bag, const BagHead& head, int lane,
+                                         uint32_t wsm)
 {
     using P = Path<TY>;
-    constexpr int RPI = kWarp / LPR;            // rows in flight per pass of the warp
-    constexpr int NF = 16 / RPI;                // finished slots per lane after the reduce-scatter
-    constexpr int UNROLL = (TY == TBE_B200_FP32) ? 1 : 2;
+    constexpr int RPI = kWarp / LPR;                                   // rows per pass of the warp
+    constexpr int UC = (P::kPasses < kWarp / RPI) ? P::kPasses : (kWarp / RPI);   // passes per chunk
+    constexpr int RC = UC * RPI;                                       // rows per chunk (divides 32)
+    constexpr int NF = 16 / RPI;                                       // finished slots per lane after the reduce-scatter
+    static_assert(UC * kWarp * P::kSlotBytes <= kChunkBytes && UC <= kMaxPasses, "chunk does not fit its buffer");
     const int k = lane % LPR;
     const int g = lane / LPR;
     const IdxT* indices = static_cast<const IdxT*>(p.indices) + bag.start;
     const float* pw = p.pw ? p.pw + bag.start : nullptr;
     const bool wrap_row = P::can_wrap(bag.D);
     const int nunits = P::units(bag.D, wrap_row);
+    const int nchunks = (bag.L + RC - 1) / RC;
+    const uint32_t slot0 = wsm + lane * P::kSlotBytes;
+    const uint32_t side0 = wsm + 2 * kChunkBytes + g * 4;
 
     for (int ublk = 0; ublk < nunits; ublk += LPR) {
         LaneCtx cx;
         cx.unit = ublk + k;
         cx.D = bag.D;
+        cx.k = k;
         // FP16/FP32 units interleave their chunks, so those paths bound-check per chunk instead.
         cx.active = (TY == TBE_B200_FP16 || TY == TBE_B200_FP32) ? true : (cx.unit < nunits);
         cx.first_blk = (ublk == 0);
@@ -402,38 +488,54 @@ __device__ __forceinline__ void pool_bag(const LookupParams& p, const BagInfo& b
         for (int j = 0; j < 16; ++j) acc[j] = 0.0f;
         float bias_acc = 0.0f;
 
-        for (int base = 0; base < bag.L; base += kWarp) {
-            const int nb = min(kWarp, bag.L - base);
-            int64_t my_idx = -1;
-            float my_w = 1.0f;
-            if (lane < nb) {
-                my_idx = static_cast<int64_t>(ld_stream(indices + base + lane));
-                if (pw) my_w = ld_stream(pw + base + lane);
-                if (my_idx < -1 && p.error_flag) atomicOr(p.error_flag, 1);
+        // The 32 indices the lanes currently hold cover rows [batch0, batch0 + 32) of the bag.
+        int batch0 = 0;
+        if (head.idx < -1 && p.error_flag && cx.first_blk) atomicOr(p.error_flag, 1);
+        int64_t my_idx = head.idx;
+        float my_w = head.w;
+        float w_buf0 = 0.0f, w_buf1 = 0.0f;   // per staging buffer: weight of row (chunk start + lane), 0 if not to be added
+
+        auto issue_chunk = [&](int c) {
+            const int row0 = c * RC;
+            if (row0 >= batch0 + kWarp) {
+                batch0 += kWarp;
+                const BagHead nb = load_batch<IdxT>(indices + batch0, pw ? pw + batch0 : nullptr, bag.L - batch0, lane, p.error_flag);
+                my_idx = nb.idx;
+                my_w = nb.w;
+                if (my_idx < -1 && p.error_flag && cx.first_blk) atomicOr(p.error_flag, 1);
             }
-            const int npass = (nb + RPI - 1) / RPI;
-            for (int pass = 0; pass < npass; pass += UNROLL) {
-                typename P::Regs regs[UNROLL];
-                float w[UNROLL];
+            const uint32_t slot = slot0 + (c & 1) * kChunkBytes;
+            const uint32_t side = side0 + (c & 1) * (kMaxPasses * 16 * 4);
+            const int rel0 = row0 - batch0;   // position of the chunk's first row among the 32 held indices
 #pragma unroll
-                for (int u = 0; u < UNROLL; ++u) {
-                    const int r = (pass + u) * RPI + g;
-                    int64_t idx;
-                    if constexpr (sizeof(IdxT) == 8) {
-                        const uint32_t lo = __shfl_sync(kFull, static_cast<uint32_t>(my_idx), r & 31);
-                        const uint32_t hi = __shfl_sync(kFull, static_cast<uint32_t>(my_idx >> 32), r & 31);
-                        idx = static_cast<int64_t>((static_cast<uint64_t>(hi) << 32) | lo);
-                    } else {
-                        idx = static_cast<int64_t>(__shfl_sync(kFull, static_cast<int32_t>(my_idx), r & 31));
-                    }
-                    w[u] = __shfl_sync(kFull, my_w, r & 31);
-                    const bool ok = (r < nb) && (idx >= 0);
-                    if (!ok) w[u] = 0.0f;
-                    path_load<TY, LPR>(regs[u], bag.table + idx * bag.stride, cx, ok);
-                }
-#pragma unroll
-                for (int u = 0; u < UNROLL; ++u) P::template accum<LPR>(regs[u], cx, w[u], acc, bias_acc);
+            for (int u = 0; u < UC; ++u) {
+                const int r = rel0 + u * RPI + g;
+                const int64_t idx = shfl_idx<IdxT>(my_idx, r & 31);
+                const bool ok = (row0 + u * RPI + g < bag.L) && (idx >= 0);
+                P::template issue<LPR>(slot + u * kWarp * P::kSlotBytes, side + u * 16 * 4, bag.table + idx * bag.stride,
+                                       bag.table, cx, ok);
             }
+            cp_async_commit();
+            // weight of row (row0 + lane) for the lanes that stand for a row of this chunk
+            const int64_t li = shfl_idx<IdxT>(my_idx, (rel0 + lane) & 31);
+            float lw = __shfl_sync(kFull, my_w, (rel0 + lane) & 31);
+            if (lane >= RC || row0 + lane >= bag.L || li < 0) lw = 0.0f;
+            if (c & 1) w_buf1 = lw; else w_buf0 = lw;
+        };
+
+        if (nchunks > 0) issue_chunk(0);
+        if (nchunks > 1) issue_chunk(1);
+        for (int c = 0; c < nchunks; ++c) {
+            if (c + 1 < nchunks) cp_async_wait<1>(); else cp_async_wait<0>();
+            const uint32_t slot = slot0 + (c & 1) * kChunkBytes;
+            const uint32_t side = side0 + (c & 1) * (kMaxPasses * 16 * 4);
+            const float wb = (c & 1) ? w_buf1 : w_buf0;
+#pragma unroll
+            for (int u = 0; u < UC; ++u) {
+                const float w = __shfl_sync(kFull, wb, u * RPI + g);
+                P::template accum<LPR>(slot + u * kWarp * P::kSlotBytes, side + u * 16 * 4, cx, w, acc, bias_acc);
+            }
+            if (c + 2 < nchunks) issue_chunk(c + 2);
         }
 
         // Combine the RPI groups: after this every lane holds NF finished slots,
@@ -453,7 +555,7 @@ __device__ __forceinline__ void pool_bag(const LookupParams& p, const BagInfo& b
 #pragma unroll
             for (int q = 0; q < NF / W; ++q) {
                 const int slot = slot_base + q * W;
-                const int e0 = path_elem<TY, LPR>(cx, slot);
+                const int e0 = P::template elem<LPR>(cx, slot);
                 if (e0 >= 0 && e0 < bag.D) {
                     float v[W];
 #pragma unroll
@@ -466,15 +568,16 @@ __device__ __forceinline__ void pool_bag(const LookupParams& p, const BagInfo& b
 }
 
 template <int TY, typename IdxT>
-__device__ __forceinline__ void pool_bag_by_width(const LookupParams& p, const BagInfo& bag, int lane)
+__device__ __forceinline__ void pool_bag_by_width(const LookupParams& p, const BagInfo& bag, const BagHead& head, int lane,
+                                                  uint32_t wsm)
 {
     const bool wrap = Path<TY>::can_wrap(bag.D);
     const int nunits = Path<TY>::units(bag.D, wrap);
-    if (nunits <= 2) pool_bag<TY, 2, IdxT>(p, bag, lane);
-    else if (nunits <= 4) pool_bag<TY, 4, IdxT>(p, bag, lane);
-    else if (nunits <= 8) pool_bag<TY, 8, IdxT>(p, bag, lane);
-    else if (nunits <= 16) pool_bag<TY, 16, IdxT>(p, bag, lane);
-    else pool_bag<TY, 32, IdxT>(p, bag, lane);
+    if (nunits <= 2) pool_bag<TY, 2, IdxT>(p, bag, head, lane, wsm);
+    else if (nunits <= 4) pool_bag<TY, 4, IdxT>(p, bag, head, lane, wsm);
+    else if (nunits <= 8) pool_bag<TY, 8, IdxT>(p, bag, head, lane, wsm);
+    else if (nunits <= 16) pool_bag<TY, 16, IdxT>(p, bag, head, lane, wsm);
+    else pool_bag<TY, 32, IdxT>(p, bag, head, lane, wsm);
 }
 
 // ---- byte-wise path (any alignment, any D, every type) ----------------------
@@ -558,70 +661,127 @@ __device__ __noinline__ void pool_bag_bytewise(const IdxT* indices, const float*
 // ---- kernels -----------------------------------------------------------------
 
 constexpr int kWarpsPerBlock = 4;
-constexpr int kMinBlocksPerSM = 8;   // caps the pooled kernel at 64 registers: 32 resident warps per SM
+constexpr int kMinBlocksPerSM = 10;   // default: 40 resident warps per SM (48 registers, 5 KB of staging memory per warp)
 
-template <typename IdxT>
-__global__ void __launch_bounds__(kWarpsPerBlock* kWarp, kMinBlocksPerSM)
+// Description of the table a bag belongs to; reloaded only when the warp moves on to another table.
+struct TableMeta {
+    const uint8_t* table;   // first row
+    int64_t stride;         // bytes per row
+    int64_t col;            // output column of the table
+    int32_t ty;
+    int32_t D;
+    bool rows_aligned;      // table start and row stride are multiples of 16 bytes
+};
+
+__device__ __forceinline__ TableMeta load_meta(const LookupParams& p, int t)
+{
+    TableMeta m;
+    m.ty = p.weights_tys[t];
+    const int d0 = p.D_offsets[t];
+    m.D = p.D_offsets[t + 1] - d0;
+    m.table = p.dev_weights + p.weights_offsets[t];
+    m.col = p.out_cols ? p.out_cols[t] : static_cast<int64_t>(d0);
+    m.stride = row_bytes_of(m.ty, m.D, p.row_alignment);
+    m.rows_aligned = ((reinterpret_cast<uintptr_t>(m.table) | static_cast<uint64_t>(m.stride)) & 15) == 0;
+    return m;
+}
+
+__device__ __forceinline__ void prefetch_l2(const void* p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
+
+// Persistent grid.  The T*B bags (bag i = t*B + b) are cut into one contiguous span per warp, so a warp
+// walks `offsets`, `indices` and the per-sample weights front to back: the bag boundaries and the
+// table description stay in L1, and the index stream is pulled into L2 a few lines ahead of use.
+// The only full-latency wait left per bag is the one for its rows, all of which (up to two chunks)
+// are in flight at once.
+template <typename IdxT, int MINB>
+__global__ void __launch_bounds__(kWarpsPerBlock* kWarp, MINB)
 tbe_pooled_kernel(const LookupParams p)
 {
+    __shared__ __align__(16) uint8_t smem[kWarpsPerBlock * kWarpSmemBytes];
     const int lane = threadIdx.x & 31;
-    const int64_t i = static_cast<int64_t>(blockIdx.x) * kWarpsPerBlock + (threadIdx.x >> 5);
-    if (i >= p.num_bags) return;
+    const int warp = threadIdx.x >> 5;
+    const uint32_t wsm = smem_u32(smem) + warp * kWarpSmemBytes;
+    const int64_t nw = static_cast<int64_t>(gridDim.x) * kWarpsPerBlock;
+    const int64_t gw = static_cast<int64_t>(blockIdx.x) * kWarpsPerBlock + warp;
+    const int64_t span_lo = p.num_bags / nw * gw + min(gw, p.num_bags % nw);
+    const int64_t span_hi = span_lo + p.num_bags / nw + (gw < p.num_bags % nw ? 1 : 0);
+    if (span_lo >= span_hi) return;
+    const IdxT* offsets = static_cast<const IdxT*>(p.offsets);
+    const IdxT* indices = static_cast<const IdxT*>(p.indices);
+    const int esz = (p.out_ty == TBE_B200_FP32) ? 4 : 2;
+    constexpr int kAhead = 128 / static_cast<int>(sizeof(IdxT));   // positions per 128-byte line of indices
+
     int t;
     int64_t b;
     if (p.B32) {
-        t = static_cast<int>(static_cast<uint32_t>(i) / p.B32);
-        b = static_cast<uint32_t>(i) - static_cast<uint32_t>(t) * p.B32;
+        t = static_cast<int>(static_cast<uint32_t>(span_lo) / p.B32);
+        b = static_cast<uint32_t>(span_lo) - static_cast<uint32_t>(t) * p.B32;
     } else {
-        t = static_cast<int>(i / p.B);
-        b = i - static_cast<int64_t>(t) * p.B;
+        t = static_cast<int>(span_lo / p.B);
+        b = span_lo - static_cast<int64_t>(t) * p.B;
     }
-    const int ty = p.weights_tys[t];
-    const int d0 = p.D_offsets[t];
-    const int D = p.D_offsets[t + 1] - d0;
-    const int64_t woff = p.weights_offsets[t];
-    const IdxT* offsets = static_cast<const IdxT*>(p.offsets);
-    const int64_t start = static_cast<int64_t>(offsets[i]);
-    const int64_t end = static_cast<int64_t>(offsets[i + 1]);
+    TableMeta m = load_meta(p, t);
+    int64_t start = static_cast<int64_t>(offsets[span_lo]);
 
-    BagInfo bag;
-    bag.table = p.dev_weights + woff;
-    bag.stride = row_bytes_of(ty, D, p.row_alignment);
-    bag.start = start;
-    bag.L = static_cast<int>(end - start);
-    bag.D = D;
-    bag.mean_mul = (p.pooling_mode == TBE_B200_POOL_MEAN && bag.L > 0) ? 1.0f / static_cast<float>(bag.L) : 1.0f;
-    const int64_t col = p.out_cols ? p.out_cols[t] : static_cast<int64_t>(d0);
-    const int esz = (p.out_ty == TBE_B200_FP32) ? 4 : 2;
-    char* dst;
-    int64_t brow = b;
-    if (p.dests) {
-        const int64_t which = b / p.rows_per_dest;
-        brow = b - which * p.rows_per_dest;
-        dst = static_cast<char*>(p.dests[which]);
-    } else {
-        dst = static_cast<char*>(p.output);
-    }
-    bag.seg = dst + (brow * p.out_stride + col) * esz;
-    bag.seg_aligned = (reinterpret_cast<uintptr_t>(bag.seg) & 15) == 0;
-    if (D <= 0) return;
+    for (int64_t i = span_lo; i < span_hi; ++i) {
+        const int64_t end = static_cast<int64_t>(offsets[i + 1]);
+        const int L = static_cast<int>(end - start);
+        const BagHead head = load_batch<IdxT>(indices + start, p.pw ? p.pw + start : nullptr, min(L, kWarp), lane, nullptr);
+        // pull the next lines of the index (and weight) stream into L2
+        if (lane < 4) {
+            const int64_t q = start + 2 * kWarp + lane * kAhead;
+            if (q < end + 8 * kWarp) {   // stays within a few bags of the data this warp will read
+                prefetch_l2(indices + q);
+                if (p.pw) prefetch_l2(p.pw + q);
+            }
+        }
 
-    const bool rows_aligned = ((reinterpret_cast<uintptr_t>(bag.table) | static_cast<uint64_t>(bag.stride)) & 15) == 0;
-    if (rows_aligned && (D & 3) == 0) {
-        switch (ty) {
-            case TBE_B200_INT8: pool_bag_by_width<TBE_B200_INT8, IdxT>(p, bag, lane); return;
-            case TBE_B200_INT4: pool_bag_by_width<TBE_B200_INT4, IdxT>(p, bag, lane); return;
-            case TBE_B200_FP8: pool_bag_by_width<TBE_B200_FP8, IdxT>(p, bag, lane); return;
-            case TBE_B200_FP16:
-                if ((D & 7) == 0) { pool_bag_by_width<TBE_B200_FP16, IdxT>(p, bag, lane); return; }
-                break;
-            case TBE_B200_FP32: pool_bag_by_width<TBE_B200_FP32, IdxT>(p, bag, lane); return;
-            default: break;
+        BagInfo bag;
+        bag.table = m.table;
+        bag.stride = m.stride;
+        bag.start = start;
+        bag.L = L;
+        bag.D = m.D;
+        bag.mean_mul = (p.pooling_mode == TBE_B200_POOL_MEAN && L > 0) ? 1.0f / static_cast<float>(L) : 1.0f;
+        char* dst;
+        int64_t brow = b;
+        if (p.dests) {
+            const int64_t which = b / p.rows_per_dest;
+            brow = b - which * p.rows_per_dest;
+            dst = static_cast<char*>(p.dests[which]);
+        } else {
+            dst = static_cast<char*>(p.output);
+        }
+        bag.seg = dst + (brow * p.out_stride + m.col) * esz;
+        bag.seg_aligned = (reinterpret_cast<uintptr_t>(bag.seg) & 15) == 0;
+
+        if (m.D > 0) {
+            bool done = false;
+            if (m.rows_aligned && (m.D & 3) == 0) {
+                done = true;
+                switch (m.ty) {
+                    case TBE_B200_INT8: pool_bag_by_width<TBE_B200_INT8, IdxT>(p, bag, head, lane, wsm); break;
+                    case TBE_B200_INT4: pool_bag_by_width<TBE_B200_INT4, IdxT>(p, bag, head, lane, wsm); break;
+                    case TBE_B200_FP8: pool_bag_by_width<TBE_B200_FP8, IdxT>(p, bag, head, lane, wsm); break;
+                    case TBE_B200_FP16:
+                        if ((m.D & 7) == 0) pool_bag_by_width<TBE_B200_FP16, IdxT>(p, bag, head, lane, wsm);
+                        else done = false;
+                        break;
+                    case TBE_B200_FP32: pool_bag_by_width<TBE_B200_FP32, IdxT>(p, bag, head, lane, wsm); break;
+                    default: done = false; break;
+                }
+            }
+            if (!done)
+                pool_bag_bytewise<IdxT>(indices + start, p.pw ? p.pw + start : nullptr, p.error_flag, bag.table, bag.stride,
+                                        L, m.D, bag.seg, bag.mean_mul, m.ty, p.out_ty, p.fp8_shift, p.fp8_mult, lane);
+        }
+        start = end;
+        if (++b == p.B) {
+            b = 0;
+            ++t;
+            if (i + 1 < span_hi) m = load_meta(p, t);
         }
     }
-    pool_bag_bytewise<IdxT>(static_cast<const IdxT*>(p.indices) + bag.start, p.pw ? p.pw + bag.start : nullptr,
-                            p.error_flag, bag.table, bag.stride, bag.L, bag.D, bag.seg, bag.mean_mul, ty, p.out_ty,
-                            p.fp8_shift, p.fp8_mult, lane);
 }
 
 // Pooling NONE: one warp per position n of `indices`; row n of the output gets the
@@ -659,6 +819,39 @@ tbe_nobag_kernel(const LookupParams p, int64_t num_indices, int max_D)
     for (int e = lane; e < D; e += kWarp)
         store_scalar(seg, e, decode_elem(row, ty, e, scale, bias, p.fp8_shift, p.fp8_mult), p.out_ty);
     for (int e = D + lane; e < max_D; e += kWarp) store_scalar(seg, e, 0.0f, p.out_ty);
+}
+
+// Occupancy variant of the pooled kernel: 10 blocks per SM by default; TBE_B200_BLOCKS_PER_SM=8 selects the
+// build with 64 registers per thread (read once per process; a tuning aid, same results either way).
+int occupancy_variant()
+{
+    static int v = 0;
+    if (v == 0) {
+        const char* e = getenv("TBE_B200_BLOCKS_PER_SM");
+        v = (e && atoi(e) == 8) ? 8 : kMinBlocksPerSM;
+    }
+    return v;
+}
+
+template <typename IdxT, int MINB>
+int launch_pooled(const LookupParams& p, cudaStream_t s)
+{
+    static int resident = 0;   // blocks that fit on one SM (occupancy query, once)
+    if (resident == 0) {
+        int n = 0;
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, tbe_pooled_kernel<IdxT, MINB>, kWarpsPerBlock * kWarp, 0) != cudaSuccess || n <= 0) {
+            (void)cudaGetLastError();
+            n = MINB;
+        }
+        resident = n;
+    }
+    // Persistent launch: as many blocks as stay resident (a multiple of the SM count), each warp striding
+    // over the bags; fewer when there are fewer bags than warps.
+    const int64_t need = (p.num_bags + kWarpsPerBlock - 1) / kWarpsPerBlock;
+    const int64_t fit = static_cast<int64_t>(sm_count()) * resident;
+    const unsigned blocks = static_cast<unsigned>(need < fit ? need : fit);
+    tbe_pooled_kernel<IdxT, MINB><<<blocks, kWarpsPerBlock * kWarp, 0, s>>>(p);
+    return check_launch("tbe_pooled_kernel");
 }
 
 }  // namespace
@@ -725,11 +918,7 @@ extern "C" int tbe_b200_int_nbit_lookup(const tbe_b200_lookup_args* a, tbe_b200_
         return check_launch("tbe_nobag_kernel");
     }
     if (p.num_bags == 0) return TBE_B200_OK;
-    const int64_t blocks = (p.num_bags + kWarpsPerBlock - 1) / kWarpsPerBlock;
-    if (blocks > 0x7fffffffll) return fail(TBE_B200_ERR_UNSUPPORTED, "lookup: T*B too large for one launch");
-    if (a->index_bits == 32)
-        tbe_pooled_kernel<int32_t><<<static_cast<unsigned>(blocks), kWarpsPerBlock * kWarp, 0, s>>>(p);
-    else
-        tbe_pooled_kernel<int64_t><<<static_cast<unsigned>(blocks), kWarpsPerBlock * kWarp, 0, s>>>(p);
-    return check_launch("tbe_pooled_kernel");
+    if (occupancy_variant() == 8)
+        return a->index_bits == 32 ? launch_pooled<int32_t, 8>(p, s) : launch_pooled<int64_t, 8>(p, s);
+    return a->index_bits == 32 ? launch_pooled<int32_t, kMinBlocksPerSM>(p, s) : launch_pooled<int64_t, kMinBlocksPerSM>(p, s);
 }

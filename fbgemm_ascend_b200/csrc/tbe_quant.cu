@@ -26,6 +26,23 @@ __device__ __forceinline__ float load_in<float>(const float* p) { return __ldg(p
 template <>
 __device__ __forceinline__ float load_in<__half>(const __half* p) { return __half2float(__ldg(p)); }
 
+// Writes the 4-byte row header (two fp16 bit patterns) at `o`.  `h` is first pinned in a 32-bit
+// register: byte stores fed straight from the 16-bit result of the float->half conversion came out
+// with a zero low byte on sm_100a (CUDA 12.9), while the same stores from a 32-bit value are correct.
+__device__ __forceinline__ void store_header(uint8_t* o, uint32_t lo16, uint32_t hi16)
+{
+    uint32_t h = (lo16 & 0xffffu) | (hi16 << 16);
+    asm volatile("" : "+r"(h));
+    if ((reinterpret_cast<uintptr_t>(o) & 3) == 0) {
+        *reinterpret_cast<uint32_t*>(o) = h;
+    } else {
+        o[0] = static_cast<uint8_t>(h & 0xffu);
+        o[1] = static_cast<uint8_t>((h >> 8) & 0xffu);
+        o[2] = static_cast<uint8_t>((h >> 16) & 0xffu);
+        o[3] = static_cast<uint8_t>(h >> 24);
+    }
+}
+
 template <int LPR>
 __device__ __forceinline__ void group_minmax(float& mn, float& mx)
 {
@@ -104,10 +121,7 @@ quantize_8bit_kernel(const InT* __restrict__ in, int64_t N, int64_t D, uint8_t* 
         }
     }
     if (TABLE) {
-        if (k == 0) {
-            const uint32_t h = f32_to_f16_bits(scale) | (f32_to_f16_bits(mn) << 16);
-            o[0] = h & 0xff; o[1] = (h >> 8) & 0xff; o[2] = (h >> 16) & 0xff; o[3] = (h >> 24) & 0xff;
-        }
+        if (k == 0) store_header(o, f32_to_f16_bits(scale), f32_to_f16_bits(mn));
         for (int64_t c = 4 + D + k; c < out_stride; c += LPR) o[c] = 0;
     } else if (k == 0) {
         const uint32_t sb[2] = {__float_as_uint(scale), __float_as_uint(mn)};
@@ -206,9 +220,7 @@ quantize_nbit_kernel(const float* __restrict__ in, int64_t N, int64_t D, uint8_t
         codes[b] = static_cast<uint8_t>(byte);
     }
     if (k == 0) {
-        const uint32_t h = __half_as_ushort(scale_h) | (static_cast<uint32_t>(__half_as_ushort(bias_h)) << 16);
-        uint8_t* hp = TABLE ? o : o + pbytes;
-        hp[0] = h & 0xff; hp[1] = (h >> 8) & 0xff; hp[2] = (h >> 16) & 0xff; hp[3] = (h >> 24) & 0xff;
+        store_header(TABLE ? o : o + pbytes, __half_as_ushort(scale_h), __half_as_ushort(bias_h));
     }
     if (TABLE)
         for (int64_t c = 4 + pbytes + k; c < out_stride; c += LPR) o[c] = 0;
@@ -253,13 +265,13 @@ pack_rows_kernel(const uint8_t* __restrict__ fused, int64_t N, int64_t pbytes, i
             uint32_t sb[2] = {0u, 0u};
 #pragma unroll
             for (int j = 0; j < 8; ++j) sb[j >> 2] |= static_cast<uint32_t>(__ldg(f + pbytes + j)) << (8 * (j & 3));
-            h = f32_to_f16_bits(__uint_as_float(sb[0])) | (f32_to_f16_bits(__uint_as_float(sb[1])) << 16);
+            h = (f32_to_f16_bits(__uint_as_float(sb[0])) & 0xffffu) | (f32_to_f16_bits(__uint_as_float(sb[1])) << 16);
         } else {
             h = 0;
 #pragma unroll
             for (int j = 0; j < 4; ++j) h |= static_cast<uint32_t>(__ldg(f + pbytes + j)) << (8 * j);
         }
-        o[0] = h & 0xff; o[1] = (h >> 8) & 0xff; o[2] = (h >> 16) & 0xff; o[3] = (h >> 24) & 0xff;
+        store_header(o, h & 0xffffu, h >> 16);
     }
     for (int64_t c = lane; c < pbytes; c += 32) o[4 + c] = __ldg(f + c);
     for (int64_t c = 4 + pbytes + lane; c < row_bytes; c += 32) o[c] = 0;
@@ -274,10 +286,16 @@ cast_fp16_rows_kernel(const float* __restrict__ in, int64_t N, int64_t D, int64_
     if (r >= N) return;
     const float* x = in + r * D;
     uint8_t* o = rows + r * row_bytes;
+    const bool even = (reinterpret_cast<uintptr_t>(o) & 1) == 0;
     for (int64_t c = lane; c < D; c += 32) {
-        const uint32_t h = f32_to_f16_bits(__ldg(x + c));
-        o[2 * c] = h & 0xff;
-        o[2 * c + 1] = (h >> 8) & 0xff;
+        uint32_t h = f32_to_f16_bits(__ldg(x + c));
+        asm volatile("" : "+r"(h));   // see store_header
+        if (even) {
+            *reinterpret_cast<unsigned short*>(o + 2 * c) = static_cast<unsigned short>(h);
+        } else {
+            o[2 * c] = static_cast<uint8_t>(h & 0xffu);
+            o[2 * c + 1] = static_cast<uint8_t>((h >> 8) & 0xffu);
+        }
     }
     for (int64_t c = 2 * D + lane; c < row_bytes; c += 32) o[c] = 0;
 }
