@@ -220,7 +220,7 @@ def run_single_gpu(args):
     from fbgemm_ascend_b200.types import SparseType
 
     name = "c2" if args.workload == "auto" else args.workload
-    ws = W.spec(name)
+    ws = W.spec(name, scale_E=args.scale_e, scale_B=args.scale_b)
     dev = torch.device("cuda:0")
     torch.cuda.set_device(dev)
     stream = torch.cuda.current_stream()
@@ -264,7 +264,7 @@ def run_single_gpu(args):
     achieved = alg_bytes / (kern_ms * 1e-3) / 1e9
 
     # end to end: host buffers in pinned memory, H2D of the request, lookup, D2H of the pooled output
-    e2e = run_e2e(tables, batches, ws, args, stream)
+    e2e = None if args.no_e2e else run_e2e(tables, batches, ws, args, stream)
 
     cpu = None
     if not args.no_cpu:
@@ -288,6 +288,7 @@ def run_single_gpu(args):
                                f"{sorted(set(t.name for t in ws.tys))}, B={ws.B}, L={ws.length_dist}, idx={ws.index_dist} "
                                f"{str(ws.index_dtype).split('.')[-1]}, pool={ws.pooling.name}, out={SparseType(ws.output_dtype).name}",
                    "rows_per_step": rows / args.steps, "table_bytes": W.table_bytes(ws),
+                   "scale_e": args.scale_e, "scale_b": args.scale_b,
                    "l2_policy": f"tables ({W.table_bytes(ws) / 1e9:.2f} GB) larger than L2; {n_batches} distinct request "
                                 "batches rotate, so hot rows stay L2-resident as in steady-state serving",
                    "build_s": round(t_build, 1)},
@@ -305,19 +306,20 @@ def run_single_gpu(args):
     print(json.dumps(line))
 
 
-def run_e2e(tables, batches, ws, args, stream):
+def run_e2e(tables, batches, ws, args, stream, forward=None):
     """Same metric through the operator with HOST buffers: every step copies its request (indices,
     offsets, weights) from pinned host memory, runs the lookup and reads the pooled output back
     to pinned host memory.  Three streams keep copy-in, lookup and copy-out of consecutive steps
     in flight at once (double buffering), as a serving loop would."""
     dev = tables.device
     n = len(batches)
+    forward = forward or tables.forward
     host_in = []
     for b in batches:
         host_in.append((b.indices.cpu().pin_memory(), b.offsets.cpu().pin_memory(),
                         None if b.weights is None else b.weights.cpu().pin_memory()))
     NBUF = 3
-    out0 = tables.forward(batches[0].indices, batches[0].offsets, batches[0].weights)
+    out0 = forward(batches[0].indices, batches[0].offsets, batches[0].weights)
     max_idx = max(b.num_rows for b in batches)
     dbuf = [(torch.empty(max_idx, dtype=batches[0].indices.dtype, device=dev),
              torch.empty_like(batches[0].offsets),
@@ -342,7 +344,10 @@ def run_e2e(tables, batches, ws, args, stream):
                 dw[:hw.numel()].copy_(hw, non_blocking=True)
             ev_in[k].record(s_in)
         stream.wait_event(ev_in[k])
-        out = tables.forward(di[:hi.numel()], do_, None if hw is None else dw[:hw.numel()])
+        # an output may live in a buffer that is rewritten two steps later (the sharded path double-buffers
+        # its peer-visible result): the read-back of step i-2 must be over before step i runs
+        stream.wait_event(ev_out[(i - 2) % NBUF])
+        out = forward(di[:hi.numel()], do_, None if hw is None else dw[:hw.numel()])
         ev_k[k].record(stream)
         with torch.cuda.stream(s_out):
             s_out.wait_event(ev_k[k])
@@ -377,6 +382,11 @@ def main():
     ap.add_argument("--workload", default="auto", choices=["auto", "c1", "c2", "c3", "c4", "c5"])
     ap.add_argument("--batches", type=int, default=8, help="distinct request batches that rotate")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg")
+    ap.add_argument("--exchange", default="both", choices=["both", "direct", "nccl"],
+                    help="multi-GPU: peer-store epilogue, NCCL all-to-all + permute kernel, or time both")
+    ap.add_argument("--scale-e", type=float, default=1.0, help="scale rows per table (small cases for profiling)")
+    ap.add_argument("--scale-b", type=float, default=1.0, help="scale the batch size (small cases for profiling)")
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
     args = ap.parse_args()
     if args.impl == "reference":

@@ -37,6 +37,8 @@ EXPORTS = {
     "tbe_b200_pack_table_rows": (_i32, [_i32, _vp, _i64, _i64, _i64, _vp, _vp]),
     "tbe_b200_quantize_to_table_rows": (_i32, [_i32, _vp, _i64, _i64, _i64, _vp, _vp]),
     "tbe_b200_permute_pooled_embs": (_i32, [_vp, _i64, _i64, _i32, _i64, _i64, _vp, _vp, _vp, _i32, _vp, _vp, _vp]),
+    "tbe_b200_permute_pooled_embs_blocked": (_i32, [_vp, _i64, _i64, _i32, _i64, _i64, _i64, _i64, _vp, _vp, _vp, _i32, _vp,
+                                                    _vp, _vp]),
     "tbe_b200_last_error": (C.c_char_p, []),
     "tbe_b200_version": (_i32, []),
 }
@@ -144,3 +146,16 @@ def quantize_to_table_rows(x: torch.Tensor, weight_ty: int, row_bytes_: int, row
     check(lib().tbe_b200_quantize_to_table_rows(int(weight_ty), _ptr(x), x.shape[0], x.shape[1], row_bytes_,
                                                 _ptr(rows_out), _stream()), "tbe_b200_quantize_to_table_rows")
     return rows_out
+
+
+def permute_pooled_embs_blocked(blocks: torch.Tensor, offset_dim_list: torch.Tensor, permute_list: torch.Tensor,
+                                inv_offset_dim_list: torch.Tensor, output: torch.Tensor,
+                                error_flag: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``blocks`` is [nblocks, B, block_cols] (contiguous); the logical source is their concatenation along
+    the columns, [B, nblocks * block_cols]; ``output`` is [B, nblocks * block_cols]."""
+    nblk, B, bc = blocks.shape
+    check(lib().tbe_b200_permute_pooled_embs_blocked(_ptr(blocks), B, nblk * bc, blocks.element_size(), bc, output.stride(0),
+                                                     bc, B * bc, _ptr(offset_dim_list), _ptr(permute_list),
+                                                     _ptr(inv_offset_dim_list), permute_list.numel(), _ptr(output),
+                                                     _ptr(error_flag), _stream()), "tbe_b200_permute_pooled_embs_blocked")
+    return output

@@ -49,6 +49,7 @@ struct LookupParams {
     int32_t* error_flag;
     int64_t B;
     int64_t num_bags;
+    int64_t num_indices;
     int64_t out_stride;
     int64_t rows_per_dest;
     int32_t T;
@@ -163,12 +164,65 @@ __device__ __forceinline__ uint32_t lds4(uint32_t a)
     return v;
 }
 
+// ---- dequantisation arithmetic ------------------------------------------------
+//
+// Integer -> float conversion instructions run at 16 lanes per clock per SM on sm_100a, which
+// would cap a 128-element INT8 row at 8 cycles.  Codes are therefore turned into exact fp16 values
+// with one byte permute (or mask) and one half2 subtract per pair -- 0x6400 | q is the half 1024 + q
+// -- and accumulated with the sm_100 mixed-precision FMA (fp16 * fp16 + fp32 -> fp32): the row scale
+// is stored as fp16, so code * scale is formed exactly and added to the fp32 accumulator with a
+// single rounding, as an fp32 FMA would.  With per-sample weights the scale is no longer an fp16
+// value; the codes are then widened to fp32 and an fp32 FMA with w * scale is used.
+
+// d = a(fp16) * b(fp16) + d(fp32), one rounding.  a, b: fp16 bit patterns in the low 16 bits.
+__device__ __forceinline__ void mixed_fma(float& d, uint32_t a, uint32_t b)
+{
+    asm("fma.rn.f32.f16 %0, %1, %2, %0;" : "+f"(d) : "h"(static_cast<unsigned short>(a)), "h"(static_cast<unsigned short>(b)));
+}
+
+// Two exact fp16 values (as a half2 bit pattern) from two codes already or'ed into the mantissas of
+// the half2 `magic` (0x6400: 1024, 0x5400: 64 with the code in mantissa bits 4..7).
+__device__ __forceinline__ uint32_t codes_to_half2(uint32_t packed, uint32_t magic)
+{
+    const __half2 v = __hsub2(*reinterpret_cast<const __half2*>(&packed), *reinterpret_cast<const __half2*>(&magic));
+    return *reinterpret_cast<const uint32_t*>(&v);
+}
+
+// acc[0..1] += pair (half2 bits) * scale: mixed FMA with the fp16 scale, or fp32 FMA with `ws`.
+__device__ __forceinline__ void add_pair(float& a0, float& a1, uint32_t pair, uint32_t scale_h, float ws, bool weighted)
+{
+    if (!weighted) {
+        mixed_fma(a0, pair & 0xffffu, scale_h);
+        mixed_fma(a1, pair >> 16, scale_h);
+    } else {
+        const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&pair));
+        a0 = fmaf(f.x, ws, a0);
+        a1 = fmaf(f.y, ws, a1);
+    }
+}
+
+// The same with the choice made at compile time and the two halves split inside one asm block.
+template <bool WEIGHTED>
+__device__ __forceinline__ void add_pair_t(float& a0, float& a1, uint32_t pair, unsigned short scale_h, float ws)
+{
+    if constexpr (!WEIGHTED) {
+        asm("{ .reg .b16 l, h; mov.b32 {l, h}, %2; fma.rn.f32.f16 %0, l, %3, %0; fma.rn.f32.f16 %1, h, %3, %1; }"
+            : "+f"(a0), "+f"(a1)
+            : "r"(pair), "h"(scale_h));
+    } else {
+        const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&pair));
+        a0 = fmaf(f.x, ws, a0);
+        a1 = fmaf(f.y, ws, a1);
+    }
+}
+
 // Staging memory of one warp: two chunk buffers of kChunkBytes (a lane's slot for pass u is at
-// (u*32 + lane) * slot_bytes) and, for header types, one 4-byte side slot per (buffer, pass, group).
+// (u*32 + lane) * slot_bytes) and, for header types, one 4-byte side slot per (buffer, pass, lane).
 constexpr int kChunkBytes = 2048;
 constexpr int kMaxPasses = 8;
-constexpr int kSideBytes = 2 * kMaxPasses * 16 * 4;
-constexpr int kWarpSmemBytes = 2 * kChunkBytes + kSideBytes;
+constexpr int kSideBytes = 2 * kMaxPasses * kWarp * 4;
+constexpr int kNextBytes = kWarp * 8 + kWarp * 4 + 16;   // next bag: 32 indices, 32 weights, end offset
+constexpr int kWarpSmemBytes = 2 * kChunkBytes + kSideBytes + kNextBytes;
 
 struct LaneCtx {
     int unit;        // 16-slot unit handled by this lane in the current block
@@ -177,6 +231,7 @@ struct LaneCtx {
     bool active;     // this unit exists in the row
     bool wrap;       // INT8/INT4 header lane that also takes the row's tail
     bool first_blk;  // block 0: the header is the first word of unit 0
+    bool weighted;   // per-sample weights are in use
     uint32_t fp8_shift;
     float fp8_mult;
 };
@@ -212,16 +267,18 @@ struct Path<TBE_B200_INT8> {
             if (cx.wrap) v.x = s; else hdr = s;
         }
         hdr = __shfl_sync(kFull, hdr, 0, LPR);
-        const float s = half_bits_to_float(hdr & 0xffffu) * w;
-        bias_acc = fmaf(half_bits_to_float(hdr >> 16), w, bias_acc);
+        // A row that must not be added has zero-filled data and header, so its scale and bias are 0.
+        const uint32_t scale_h = hdr & 0xffffu;
+        const float ws = half_bits_to_float(scale_h) * w;
+        bias_acc = fmaf(half_bits_to_float(hdr >> 16), cx.weighted ? w : 1.0f, bias_acc);
         const uint32_t words[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const float q = static_cast<float>((words[i] >> (8 * j)) & 0xffu);
-                acc[4 * i + j] = fmaf(q, s, acc[4 * i + j]);
-            }
+            // bytes (q0, 0x64, q1, 0x64) = half2(1024 + q0, 1024 + q1)
+            const uint32_t lo = codes_to_half2(__byte_perm(words[i], 0x64646464u, 0x4140), 0x64006400u);
+            const uint32_t hi = codes_to_half2(__byte_perm(words[i], 0x64646464u, 0x4342), 0x64006400u);
+            add_pair(acc[4 * i + 0], acc[4 * i + 1], lo, scale_h, ws, cx.weighted);
+            add_pair(acc[4 * i + 2], acc[4 * i + 3], hi, scale_h, ws, cx.weighted);
         }
     }
     template <int LPR>
@@ -258,16 +315,23 @@ struct Path<TBE_B200_INT4> {
             if (cx.wrap) v.x = s; else hdr = s;
         }
         hdr = __shfl_sync(kFull, hdr, 0, LPR);
-        const float s = half_bits_to_float(hdr & 0xffffu) * w;
-        bias_acc = fmaf(half_bits_to_float(hdr >> 16), w, bias_acc);
+        const uint32_t scale_h = hdr & 0xffffu;
+        const float ws = half_bits_to_float(scale_h) * w;
+        bias_acc = fmaf(half_bits_to_float(hdr >> 16), cx.weighted ? w : 1.0f, bias_acc);
         const uint32_t words[2] = {v.x, v.y};
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                const float q = static_cast<float>((words[i] >> (4 * j)) & 0xfu);
-                acc[8 * i + j] = fmaf(q, s, acc[8 * i + j]);
-            }
+            // nibble pairs (j, j + 4) sit 16 bits apart: mask them into two half mantissas at once.
+            // 0x6400 | n = 1024 + n; 0x5400 | (n << 4) = 64 + n.
+            const uint32_t x = words[i], y = words[i] >> 8;
+            const uint32_t p0 = codes_to_half2((x & 0x000F000Fu) | 0x64006400u, 0x64006400u);   // nibbles 0, 4
+            const uint32_t p1 = codes_to_half2((x & 0x00F000F0u) | 0x54005400u, 0x54005400u);   // nibbles 1, 5
+            const uint32_t p2 = codes_to_half2((y & 0x000F000Fu) | 0x64006400u, 0x64006400u);   // nibbles 2, 6
+            const uint32_t p3 = codes_to_half2((y & 0x00F000F0u) | 0x54005400u, 0x54005400u);   // nibbles 3, 7
+            add_pair(acc[8 * i + 0], acc[8 * i + 4], p0, scale_h, ws, cx.weighted);
+            add_pair(acc[8 * i + 1], acc[8 * i + 5], p1, scale_h, ws, cx.weighted);
+            add_pair(acc[8 * i + 2], acc[8 * i + 6], p2, scale_h, ws, cx.weighted);
+            add_pair(acc[8 * i + 3], acc[8 * i + 7], p3, scale_h, ws, cx.weighted);
         }
     }
     template <int LPR>
@@ -340,11 +404,9 @@ struct Path<TBE_B200_FP16> {
         const uint4 a = (ca * 8 < cx.D) ? lds16(slot) : make_uint4(0u, 0u, 0u, 0u);
         const uint4 b = ((ca + LPR) * 8 < cx.D) ? lds16(slot + 16) : make_uint4(0u, 0u, 0u, 0u);
         const uint32_t words[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+        // unweighted: value * 1.0 + acc in one mixed FMA (rows not to be added are zero-filled)
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            acc[2 * i] = fmaf(w, half_bits_to_float(words[i] & 0xffffu), acc[2 * i]);
-            acc[2 * i + 1] = fmaf(w, half_bits_to_float(words[i] >> 16), acc[2 * i + 1]);
-        }
+        for (int i = 0; i < 8; ++i) add_pair(acc[2 * i], acc[2 * i + 1], words[i], 0x3c00u, w, cx.weighted);
     }
     template <int LPR>
     static __device__ __forceinline__ int elem(const LaneCtx& cx, int slot)
@@ -417,9 +479,10 @@ struct BagInfo {
     bool seg_aligned;       // seg is 16-byte aligned
 };
 
-// The first (up to) 32 indices and weights of a bag, one per lane, fetched ahead of time.
+// Up to 32 consecutive indices and weights of a bag, one per lane.  Indices are narrowed to 32 bits:
+// a row number outside [-1, 2^31) is reported through the error flag and treated as -1 (skipped).
 struct BagHead {
-    int64_t idx;   // -1 beyond the bag
+    int32_t idx;   // -1 beyond the bag
     float w;
 };
 
@@ -429,24 +492,14 @@ __device__ __forceinline__ BagHead load_batch(const IdxT* indices, const float* 
     BagHead h;
     h.idx = -1;
     h.w = 1.0f;
-    (void)error_flag;
     if (lane < n) {
-        h.idx = static_cast<int64_t>(ld_stream(indices + lane));
-        if (pw) h.w = ld_stream(pw + lane);
+        const IdxT v = __ldg(indices + lane);
+        const bool bad = (v < static_cast<IdxT>(-1)) || (sizeof(IdxT) == 8 && static_cast<int64_t>(v) > 0x7fffffffll);
+        h.idx = bad ? -1 : static_cast<int32_t>(v);
+        if (bad && error_flag) atomicOr(error_flag, 1);
+        if (pw) h.w = __ldg(pw + lane);
     }
     return h;
-}
-
-template <typename IdxT>
-__device__ __forceinline__ int64_t shfl_idx(int64_t v, int src)
-{
-    if constexpr (sizeof(IdxT) == 8) {
-        const uint32_t lo = __shfl_sync(kFull, static_cast<uint32_t>(v), src);
-        const uint32_t hi = __shfl_sync(kFull, static_cast<uint32_t>(static_cast<uint64_t>(v) >> 32), src);
-        return static_cast<int64_t>((static_cast<uint64_t>(hi) << 32) | lo);
-    } else {
-        return static_cast<int64_t>(__shfl_sync(kFull, static_cast<int32_t>(v), src));
-    }
 }
 
 // Pools one bag whose rows are 16-byte aligned with a 16-byte-multiple stride.
@@ -480,6 +533,7 @@ __device__ __forceinline__ void pool_bag(const LookupParams& p, const BagInfo& b
         cx.active = (TY == TBE_B200_FP16 || TY == TBE_B200_FP32) ? true : (cx.unit < nunits);
         cx.first_blk = (ublk == 0);
         cx.wrap = wrap_row && cx.unit == 0;
+        cx.weighted = p.pw != nullptr;
         cx.fp8_shift = p.fp8_shift;
         cx.fp8_mult = p.fp8_mult;
 
@@ -490,8 +544,7 @@ __device__ __forceinline__ void pool_bag(const LookupParams& p, const BagInfo& b
 
         // The 32 indices the lanes currently hold cover rows [batch0, batch0 + 32) of the bag.
         int batch0 = 0;
-        if (head.idx < -1 && p.error_flag && cx.first_blk) atomicOr(p.error_flag, 1);
-        int64_t my_idx = head.idx;
+        int32_t my_idx = head.idx;
         float my_w = head.w;
         float w_buf0 = 0.0f, w_buf1 = 0.0f;   // per staging buffer: weight of row (chunk start + lane), 0 if not to be added
 
@@ -499,28 +552,30 @@ __device__ __forceinline__ void pool_bag(const LookupParams& p, const BagInfo& b
             const int row0 = c * RC;
             if (row0 >= batch0 + kWarp) {
                 batch0 += kWarp;
-                const BagHead nb = load_batch<IdxT>(indices + batch0, pw ? pw + batch0 : nullptr, bag.L - batch0, lane, p.error_flag);
+                const BagHead nb = load_batch<IdxT>(indices + batch0, pw ? pw + batch0 : nullptr, bag.L - batch0, lane,
+                                                    cx.first_blk ? p.error_flag : nullptr);
                 my_idx = nb.idx;
                 my_w = nb.w;
-                if (my_idx < -1 && p.error_flag && cx.first_blk) atomicOr(p.error_flag, 1);
             }
             const uint32_t slot = slot0 + (c & 1) * kChunkBytes;
             const uint32_t side = side0 + (c & 1) * (kMaxPasses * 16 * 4);
             const int rel0 = row0 - batch0;   // position of the chunk's first row among the 32 held indices
-#pragma unroll
+#pragma unroll 1
             for (int u = 0; u < UC; ++u) {
                 const int r = rel0 + u * RPI + g;
-                const int64_t idx = shfl_idx<IdxT>(my_idx, r & 31);
+                const int32_t idx = __shfl_sync(kFull, my_idx, r & 31);
                 const bool ok = (row0 + u * RPI + g < bag.L) && (idx >= 0);
-                P::template issue<LPR>(slot + u * kWarp * P::kSlotBytes, side + u * 16 * 4, bag.table + idx * bag.stride,
-                                       bag.table, cx, ok);
+                P::template issue<LPR>(slot + u * kWarp * P::kSlotBytes, side + u * 16 * 4,
+                                       bag.table + static_cast<int64_t>(idx) * bag.stride, bag.table, cx, ok);
             }
             cp_async_commit();
-            // weight of row (row0 + lane) for the lanes that stand for a row of this chunk
-            const int64_t li = shfl_idx<IdxT>(my_idx, (rel0 + lane) & 31);
-            float lw = __shfl_sync(kFull, my_w, (rel0 + lane) & 31);
-            if (lane >= RC || row0 + lane >= bag.L || li < 0) lw = 0.0f;
-            if (c & 1) w_buf1 = lw; else w_buf0 = lw;
+            if (cx.weighted) {
+                // weight of row (row0 + lane) for the lanes that stand for a row of this chunk
+                const int32_t li = __shfl_sync(kFull, my_idx, (rel0 + lane) & 31);
+                float lw = __shfl_sync(kFull, my_w, (rel0 + lane) & 31);
+                if (lane >= RC || row0 + lane >= bag.L || li < 0) lw = 0.0f;
+                if (c & 1) w_buf1 = lw; else w_buf0 = lw;
+            }
         };
 
         if (nchunks > 0) issue_chunk(0);
@@ -530,9 +585,10 @@ __device__ __forceinline__ void pool_bag(const LookupParams& p, const BagInfo& b
             const uint32_t slot = slot0 + (c & 1) * kChunkBytes;
             const uint32_t side = side0 + (c & 1) * (kMaxPasses * 16 * 4);
             const float wb = (c & 1) ? w_buf1 : w_buf0;
-#pragma unroll
+#pragma unroll 1
             for (int u = 0; u < UC; ++u) {
-                const float w = __shfl_sync(kFull, wb, u * RPI + g);
+                // Unweighted: rows that are not to be added are zero-filled, so every row can use weight 1.
+                const float w = cx.weighted ? __shfl_sync(kFull, wb, u * RPI + g) : 1.0f;
                 P::template accum<LPR>(slot + u * kWarp * P::kSlotBytes, side + u * 16 * 4, cx, w, acc, bias_acc);
             }
             if (c + 2 < nchunks) issue_chunk(c + 2);
@@ -579,6 +635,31 @@ __device__ __forceinline__ void pool_bag_by_width(const LookupParams& p, const B
     else if (nunits <= 16) pool_bag<TY, 16, IdxT>(p, bag, head, lane, wsm);
     else pool_bag<TY, 32, IdxT>(p, bag, head, lane, wsm);
 }
+
+// Description of the table a bag belongs to; reloaded only when the warp moves on to another table.
+struct TableMeta {
+    const uint8_t* table;   // first row
+    int64_t stride;         // bytes per row
+    int64_t col;            // output column of the table
+    int32_t ty;
+    int32_t D;
+    bool rows_aligned;      // table start and row stride are multiples of 16 bytes
+};
+
+__device__ __forceinline__ TableMeta load_meta(const LookupParams& p, int t)
+{
+    TableMeta m;
+    m.ty = p.weights_tys[t];
+    const int d0 = p.D_offsets[t];
+    m.D = p.D_offsets[t + 1] - d0;
+    m.table = p.dev_weights + p.weights_offsets[t];
+    m.col = p.out_cols ? p.out_cols[t] : static_cast<int64_t>(d0);
+    m.stride = row_bytes_of(m.ty, m.D, p.row_alignment);
+    m.rows_aligned = ((reinterpret_cast<uintptr_t>(m.table) | static_cast<uint64_t>(m.stride)) & 15) == 0;
+    return m;
+}
+
+__device__ __forceinline__ void prefetch_l2(const void* p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
 
 // ---- byte-wise path (any alignment, any D, every type) ----------------------
 
@@ -658,84 +739,259 @@ __device__ __noinline__ void pool_bag_bytewise(const IdxT* indices, const float*
     }
 }
 
-// ---- kernels -----------------------------------------------------------------
-
-constexpr int kWarpsPerBlock = 4;
-constexpr int kMinBlocksPerSM = 10;   // default: 40 resident warps per SM (48 registers, 5 KB of staging memory per warp)
-
-// Description of the table a bag belongs to; reloaded only when the warp moves on to another table.
-struct TableMeta {
-    const uint8_t* table;   // first row
-    int64_t stride;         // bytes per row
-    int64_t col;            // output column of the table
-    int32_t ty;
-    int32_t D;
-    bool rows_aligned;      // table start and row stride are multiples of 16 bytes
-};
-
-__device__ __forceinline__ TableMeta load_meta(const LookupParams& p, int t)
+// The common INT8 / INT4 shape, written for the fewest instructions per row and the fewest exposed
+// latencies per bag.  It handles a run of consecutive bags of ONE table, so everything that depends
+// only on the table or on the lane is computed once per run: D a multiple of 16 and at most 512 means a
+// row is one block of LPR units and the header lane always takes the row's tail; the lane's byte offset
+// into a row, the tail position, the staging addresses and the output position of the lane's finished
+// elements are all loop constants.
+//   * A row address is one 32x32->64-bit multiply-add.  A row that is not to be added (index -1, or past
+//     the end of the bag) is a zero-fill copy whose address is never dereferenced; zero codes with a zero
+//     header add nothing, so no weight or predicate is needed when the rows are consumed.
+//   * The pass loops are free of divergent branches: every lane issues both copies of a pass (its 16 or
+//     8 bytes and the row's tail word; lanes with nothing to fetch copy zero bytes) and reads both back.
+//   * A round requests every row it covers (up to 32) before it consumes any, so all the rows of a
+//     typical bag are in flight together; while the warp waits for them, the indices, weights and end
+//     offset of the NEXT bag are already being loaded (their addresses only need this bag's end).
+//   * The two pass loops are rolled on purpose: one copy of each body keeps the hot code within the
+//     instruction cache.
+template <int TY, int LPR, typename IdxT, bool WEIGHTED>
+__device__ __forceinline__ void pool_run_fast(const LookupParams& p, const TableMeta& m, int64_t i0, int64_t i1, int64_t b,
+                                              int lane, uint32_t wsm)
 {
-    TableMeta m;
-    m.ty = p.weights_tys[t];
-    const int d0 = p.D_offsets[t];
-    m.D = p.D_offsets[t + 1] - d0;
-    m.table = p.dev_weights + p.weights_offsets[t];
-    m.col = p.out_cols ? p.out_cols[t] : static_cast<int64_t>(d0);
-    m.stride = row_bytes_of(m.ty, m.D, p.row_alignment);
-    m.rows_aligned = ((reinterpret_cast<uintptr_t>(m.table) | static_cast<uint64_t>(m.stride)) & 15) == 0;
-    return m;
-}
-
-__device__ __forceinline__ void prefetch_l2(const void* p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
-
-// Persistent grid.  The T*B bags (bag i = t*B + b) are cut into one contiguous span per warp, so a warp
-// walks `offsets`, `indices` and the per-sample weights front to back: the bag boundaries and the
-// table description stay in L1, and the index stream is pulled into L2 a few lines ahead of use.
-// The only full-latency wait left per bag is the one for its rows, all of which (up to two chunks)
-// are in flight at once.
-template <typename IdxT, int MINB>
-__global__ void __launch_bounds__(kWarpsPerBlock* kWarp, MINB)
-tbe_pooled_kernel(const LookupParams p)
-{
-    __shared__ __align__(16) uint8_t smem[kWarpsPerBlock * kWarpSmemBytes];
-    const int lane = threadIdx.x & 31;
-    const int warp = threadIdx.x >> 5;
-    const uint32_t wsm = smem_u32(smem) + warp * kWarpSmemBytes;
-    const int64_t nw = static_cast<int64_t>(gridDim.x) * kWarpsPerBlock;
-    const int64_t gw = static_cast<int64_t>(blockIdx.x) * kWarpsPerBlock + warp;
-    const int64_t span_lo = p.num_bags / nw * gw + min(gw, p.num_bags % nw);
-    const int64_t span_hi = span_lo + p.num_bags / nw + (gw < p.num_bags % nw ? 1 : 0);
-    if (span_lo >= span_hi) return;
+    static_assert(TY == TBE_B200_INT8 || TY == TBE_B200_INT4, "header types only");
+    constexpr bool k8 = (TY == TBE_B200_INT8);
+    constexpr int CH = k8 ? 16 : 8;                                    // bytes a lane fetches per row
+    constexpr int RPI = kWarp / LPR;                                   // rows per pass of the warp
+    constexpr int KP = (2 * kChunkBytes) / (kWarp * CH) < kMaxPasses ? (2 * kChunkBytes) / (kWarp * CH) : kMaxPasses;
+    constexpr int UR = (KP < kWarp / RPI) ? KP : (kWarp / RPI);        // passes per round
+    constexpr int RR = UR * RPI;                                       // rows per round (divides 32)
+    constexpr int NF = 16 / RPI;                                       // finished slots per lane after the reduce-scatter
+    constexpr int W = NF >= 4 ? 4 : NF;                                // elements per store
+    constexpr int HS = k8 ? 4 : 8;                                     // slots of the header lane that hold the row's tail
+    static_assert(UR * kWarp * 4 <= kSideBytes && UR * kWarp * CH <= 2 * kChunkBytes, "round does not fit the staging memory");
+    const int k = lane % LPR;
+    const int g = lane / LPR;
+    const int D = m.D;
+    const bool active = k < D / 16;        // lanes past the row's last unit have nothing to fetch (D < 16 * LPR)
+    const bool head_lane = (k == 0);
+    const uint32_t stride = static_cast<uint32_t>(m.stride);
+    const uint8_t* lane_base = m.table + k * CH;
+    const uint8_t* tail_base = m.table + (k8 ? D : D / 2);             // elements D-4.. (INT8) / D-8.. (INT4)
+    const uint32_t slot0 = wsm + lane * CH;
+    const uint32_t side0 = wsm + 2 * kChunkBytes + lane * 4;
+    const int full_bytes = active ? CH : 0;
     const IdxT* offsets = static_cast<const IdxT*>(p.offsets);
     const IdxT* indices = static_cast<const IdxT*>(p.indices);
+    const int64_t N = p.num_indices;
     const int esz = (p.out_ty == TBE_B200_FP32) ? 4 : 2;
-    constexpr int kAhead = 128 / static_cast<int>(sizeof(IdxT));   // positions per 128-byte line of indices
+    const int64_t row_bytes = p.out_stride * esz;
 
-    int t;
-    int64_t b;
-    if (p.B32) {
-        t = static_cast<int>(static_cast<uint32_t>(span_lo) / p.B32);
-        b = static_cast<uint32_t>(span_lo) - static_cast<uint32_t>(t) * p.B32;
-    } else {
-        t = static_cast<int>(span_lo / p.B);
-        b = span_lo - static_cast<int64_t>(t) * p.B;
+    // Where this lane's finished elements go: slot -> element is fixed per lane.  Unit k covers elements
+    // [16k - HS, 16k + 16 - HS); the header lane's first HS slots are the last HS elements of the row.
+    int slot_base = 0;
+    if constexpr (RPI >= 2) slot_base += ((lane >> 4) & 1) ? 8 : 0;
+    if constexpr (RPI >= 4) slot_base += ((lane >> 3) & 1) ? 4 : 0;
+    if constexpr (RPI >= 8) slot_base += ((lane >> 2) & 1) ? 2 : 0;
+    if constexpr (RPI >= 16) slot_base += ((lane >> 1) & 1) ? 1 : 0;
+    int e_first[NF / W];
+#pragma unroll
+    for (int q = 0; q < NF / W; ++q) {
+        const int slot = slot_base + q * W;
+        e_first[q] = (head_lane && slot < HS) ? (D - HS + slot) : (16 * k - HS + slot);
     }
-    TableMeta m = load_meta(p, t);
-    int64_t start = static_cast<int64_t>(offsets[span_lo]);
+    char* out_table = nullptr;             // output address of (row 0, first column of this table)
+    bool vec_ok = false;
+    if (!p.dests) {
+        out_table = static_cast<char*>(p.output) + m.col * esz;
+        vec_ok = ((reinterpret_cast<uintptr_t>(out_table) | static_cast<uint64_t>(row_bytes)) & 15) == 0;
+    }
 
-    for (int64_t i = span_lo; i < span_hi; ++i) {
-        const int64_t end = static_cast<int64_t>(offsets[i + 1]);
+    // Staging for the NEXT bag's first 32 indices and weights and its end offset.  They are fetched with
+    // cp.async, not into registers: a register that holds an outstanding load across the whole bag body
+    // gets spilled, and the spill store waits for the load -- which would serialise the two latencies.
+    const uint32_t nx_idx = wsm + 2 * kChunkBytes + kSideBytes + lane * static_cast<int>(sizeof(IdxT));
+    const uint32_t nx_w = wsm + 2 * kChunkBytes + kSideBytes + kWarp * 8 + lane * 4;
+    const uint32_t nx_end = wsm + 2 * kChunkBytes + kSideBytes + kWarp * 12;
+
+    auto request_bag_head = [&](int64_t first, int64_t bag_i) {
+        // indices[first + lane], weights[first + lane] (zero-filled past the end of the arrays), offsets[bag_i + 1]
+        const bool in = first + lane < N;
+        if constexpr (sizeof(IdxT) == 8) cp_async8(nx_idx, indices + (in ? first + lane : 0), in ? 8 : 0);
+        else cp_async4(nx_idx, indices + (in ? first + lane : 0), in ? 4 : 0);
+        if constexpr (WEIGHTED) cp_async4(nx_w, p.pw + (in ? first + lane : 0), in ? 4 : 0);
+        if (lane == 0) {
+            if constexpr (sizeof(IdxT) == 8) cp_async8(nx_end, offsets + bag_i + 1, 8);
+            else cp_async4(nx_end, offsets + bag_i + 1, 4);
+        }
+        cp_async_commit();
+    };
+
+    int64_t start = static_cast<int64_t>(__ldg(offsets + i0));
+    request_bag_head(start, i0);
+
+    for (int64_t i = i0; i < i1; ++i, ++b) {
+        cp_async_wait<0>();
+        __syncwarp();   // lane 0's copy of the end offset is read by every lane
+        IdxT raw_idx;
+        int64_t end;
+        if constexpr (sizeof(IdxT) == 8) {
+            const uint2 v = lds8(nx_idx);
+            raw_idx = static_cast<IdxT>((static_cast<uint64_t>(v.y) << 32) | v.x);
+            const uint2 e = lds8(nx_end);
+            end = static_cast<int64_t>((static_cast<uint64_t>(e.y) << 32) | e.x);
+        } else {
+            raw_idx = static_cast<IdxT>(lds4(nx_idx));
+            end = static_cast<int64_t>(static_cast<int32_t>(lds4(nx_end)));
+        }
+        float my_w = 1.0f;
+        if constexpr (WEIGHTED) my_w = __uint_as_float(lds4(nx_w));
+        __syncwarp();   // everyone has read the staging words before they are requested again
         const int L = static_cast<int>(end - start);
-        const BagHead head = load_batch<IdxT>(indices + start, p.pw ? p.pw + start : nullptr, min(L, kWarp), lane, nullptr);
-        // pull the next lines of the index (and weight) stream into L2
-        if (lane < 4) {
-            const int64_t q = start + 2 * kWarp + lane * kAhead;
-            if (q < end + 8 * kWarp) {   // stays within a few bags of the data this warp will read
-                prefetch_l2(indices + q);
-                if (p.pw) prefetch_l2(p.pw + q);
+        // The lanes hold the indices of rows [batch0, batch0 + 32) of the bag, narrowed to 32 bits.
+        int batch0 = 0;
+        int32_t my_idx;
+        {
+            const bool bad = (raw_idx < static_cast<IdxT>(-1)) || (sizeof(IdxT) == 8 && static_cast<int64_t>(raw_idx) > 0x7fffffffll);
+            my_idx = (lane < L && !bad) ? static_cast<int32_t>(raw_idx) : -1;
+            if (lane < L && bad && p.error_flag) atomicOr(p.error_flag, 1);
+        }
+        bool head_requested = false;   // the next bag's head goes out right after this bag's first round of rows
+
+        float acc[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) acc[j] = 0.0f;
+        float bias_acc = 0.0f;
+
+        for (int row0 = 0; row0 < L; row0 += RR) {
+            if (row0 >= batch0 + kWarp) {
+                batch0 += kWarp;
+                const BagHead nb = load_batch<IdxT>(indices + start + batch0, WEIGHTED ? p.pw + start + batch0 : nullptr,
+                                                    L - batch0, lane, p.error_flag);
+                my_idx = nb.idx;
+                my_w = nb.w;
+            }
+            const int npass = (min(RR, L - row0) + RPI - 1) / RPI;
+            const int src0 = (row0 - batch0) + g;   // lane holding the index of this group's row in pass 0
+            uint32_t slot = slot0, side = side0;
+#pragma unroll 1
+            for (int u = 0; u < npass; ++u) {
+                const int32_t idx = __shfl_sync(kFull, my_idx, src0 + u * RPI);
+                const bool ok = idx >= 0;
+                const uint64_t off = static_cast<uint64_t>(static_cast<uint32_t>(idx)) * stride;
+                if (k8) cp_async16(slot, lane_base + off, ok ? full_bytes : 0);
+                else cp_async8(slot, lane_base + off, ok ? full_bytes : 0);
+                cp_async4(side, tail_base + off, ok ? 4 : 0);
+                slot += kWarp * CH;
+                side += kWarp * 4;
+            }
+            cp_async_commit();
+            if (!head_requested && i + 1 < i1) {
+                // Next bag: its first indices start where this bag ends, so they can be requested now and
+                // arrive while this bag is being pooled.
+                request_bag_head(end, i + 1);
+                if (lane == 0 && end + 4 * kWarp < N) prefetch_l2(indices + end + 4 * kWarp);
+                head_requested = true;
+                cp_async_wait<1>();   // this round's rows are in; the head may still be on its way
+            } else {
+                cp_async_wait<0>();
+            }
+            slot = slot0;
+            side = side0;
+#pragma unroll 1
+            for (int u = 0; u < npass; ++u) {
+                uint32_t words[4] = {0u, 0u, 0u, 0u};
+                if (k8) {
+                    const uint4 v = lds16(slot);
+                    words[0] = v.x; words[1] = v.y; words[2] = v.z; words[3] = v.w;
+                } else {
+                    const uint2 v = lds8(slot);
+                    words[0] = v.x; words[1] = v.y;
+                }
+                const uint32_t tail = lds4(side);
+                slot += kWarp * CH;
+                side += kWarp * 4;
+                // The header is the first word of unit 0; that lane then swaps in the row's tail.
+                const uint32_t hdr = __shfl_sync(kFull, words[0], 0, LPR);
+                words[0] = head_lane ? tail : words[0];
+                const unsigned short scale_h = static_cast<unsigned short>(hdr & 0xffffu);
+                float ws = 0.0f;
+                if constexpr (WEIGHTED) {
+                    const float w = __shfl_sync(kFull, my_w, src0 + u * RPI);
+                    ws = half_bits_to_float(scale_h) * w;
+                    bias_acc = fmaf(half_bits_to_float(hdr >> 16), w, bias_acc);
+                } else {
+                    bias_acc += half_bits_to_float(hdr >> 16);
+                }
+                if (k8) {
+#pragma unroll
+                    for (int i4 = 0; i4 < 4; ++i4) {
+                        // bytes 0 and 2, then bytes 1 and 3, masked into the mantissas of half2(1024, 1024)
+                        const uint32_t even = codes_to_half2((words[i4] & 0x00FF00FFu) | 0x64006400u, 0x64006400u);
+                        const uint32_t odd = codes_to_half2(((words[i4] >> 8) & 0x00FF00FFu) | 0x64006400u, 0x64006400u);
+                        add_pair_t<WEIGHTED>(acc[4 * i4 + 0], acc[4 * i4 + 2], even, scale_h, ws);
+                        add_pair_t<WEIGHTED>(acc[4 * i4 + 1], acc[4 * i4 + 3], odd, scale_h, ws);
+                    }
+                } else {
+#pragma unroll
+                    for (int i2 = 0; i2 < 2; ++i2) {
+                        const uint32_t x = words[i2], y = words[i2] >> 8;
+                        const uint32_t p0 = codes_to_half2((x & 0x000F000Fu) | 0x64006400u, 0x64006400u);   // nibbles 0, 4
+                        const uint32_t p1 = codes_to_half2((x & 0x00F000F0u) | 0x54005400u, 0x54005400u);   // nibbles 1, 5
+                        const uint32_t p2 = codes_to_half2((y & 0x000F000Fu) | 0x64006400u, 0x64006400u);   // nibbles 2, 6
+                        const uint32_t p3 = codes_to_half2((y & 0x00F000F0u) | 0x54005400u, 0x54005400u);   // nibbles 3, 7
+                        add_pair_t<WEIGHTED>(acc[8 * i2 + 0], acc[8 * i2 + 4], p0, scale_h, ws);
+                        add_pair_t<WEIGHTED>(acc[8 * i2 + 1], acc[8 * i2 + 5], p1, scale_h, ws);
+                        add_pair_t<WEIGHTED>(acc[8 * i2 + 2], acc[8 * i2 + 6], p2, scale_h, ws);
+                        add_pair_t<WEIGHTED>(acc[8 * i2 + 3], acc[8 * i2 + 7], p3, scale_h, ws);
+                    }
+                }
             }
         }
 
+        // Combine the RPI groups (reduce-scatter over shuffles), add the pooled biases, scale for MEAN, store.
+        if constexpr (RPI >= 2) halve<16>(acc, 16, (lane >> 4) & 1);
+        if constexpr (RPI >= 4) halve<8>(acc, 8, (lane >> 3) & 1);
+        if constexpr (RPI >= 8) halve<4>(acc, 4, (lane >> 2) & 1);
+        if constexpr (RPI >= 16) halve<2>(acc, 2, (lane >> 1) & 1);
+#pragma unroll
+        for (int d = LPR; d < kWarp; d <<= 1) bias_acc += __shfl_xor_sync(kFull, bias_acc, d);
+        const float mean_mul = (p.pooling_mode == TBE_B200_POOL_MEAN && L > 0) ? 1.0f / static_cast<float>(L) : 1.0f;
+        char* seg;
+        bool vec = vec_ok;
+        if (p.dests) {
+            const int64_t which = b / p.rows_per_dest;
+            seg = static_cast<char*>(p.dests[which]) + ((b - which * p.rows_per_dest) * p.out_stride + m.col) * esz;
+            vec = (reinterpret_cast<uintptr_t>(seg) & 15) == 0;
+        } else {
+            seg = out_table + b * row_bytes;
+        }
+        if (active) {
+#pragma unroll
+            for (int q = 0; q < NF / W; ++q) {
+                float v[W];
+#pragma unroll
+                for (int j = 0; j < W; ++j) v[j] = (acc[q * W + j] + bias_acc) * mean_mul;
+                store_out<W>(seg, e_first[q], v, p.out_ty, vec);
+            }
+        }
+        if (!head_requested && i + 1 < i1) request_bag_head(end, i + 1);   // an empty bag ran no round
+        start = end;
+    }
+}
+
+// A run of bags of one table through the general per-bag code.
+template <typename IdxT>
+__device__ __forceinline__ void pool_run_general(const LookupParams& p, const TableMeta& m, int64_t i0, int64_t i1, int64_t b,
+                                                 int lane, uint32_t wsm)
+{
+    const IdxT* offsets = static_cast<const IdxT*>(p.offsets);
+    const IdxT* indices = static_cast<const IdxT*>(p.indices);
+    const int esz = (p.out_ty == TBE_B200_FP32) ? 4 : 2;
+    int64_t start = static_cast<int64_t>(offsets[i0]);
+    for (int64_t i = i0; i < i1; ++i, ++b) {
+        const int64_t end = static_cast<int64_t>(offsets[i + 1]);
+        const int L = static_cast<int>(end - start);
         BagInfo bag;
         bag.table = m.table;
         bag.stride = m.stride;
@@ -754,32 +1010,98 @@ tbe_pooled_kernel(const LookupParams p)
         }
         bag.seg = dst + (brow * p.out_stride + m.col) * esz;
         bag.seg_aligned = (reinterpret_cast<uintptr_t>(bag.seg) & 15) == 0;
-
-        if (m.D > 0) {
-            bool done = false;
-            if (m.rows_aligned && (m.D & 3) == 0) {
-                done = true;
-                switch (m.ty) {
-                    case TBE_B200_INT8: pool_bag_by_width<TBE_B200_INT8, IdxT>(p, bag, head, lane, wsm); break;
-                    case TBE_B200_INT4: pool_bag_by_width<TBE_B200_INT4, IdxT>(p, bag, head, lane, wsm); break;
-                    case TBE_B200_FP8: pool_bag_by_width<TBE_B200_FP8, IdxT>(p, bag, head, lane, wsm); break;
-                    case TBE_B200_FP16:
-                        if ((m.D & 7) == 0) pool_bag_by_width<TBE_B200_FP16, IdxT>(p, bag, head, lane, wsm);
-                        else done = false;
-                        break;
-                    case TBE_B200_FP32: pool_bag_by_width<TBE_B200_FP32, IdxT>(p, bag, head, lane, wsm); break;
-                    default: done = false; break;
-                }
+        bool done = false;
+        if (m.rows_aligned && (m.D & 3) == 0) {
+            const BagHead head = load_batch<IdxT>(indices + start, p.pw ? p.pw + start : nullptr, min(L, kWarp), lane, p.error_flag);
+            done = true;
+            switch (m.ty) {
+                case TBE_B200_INT8: pool_bag_by_width<TBE_B200_INT8, IdxT>(p, bag, head, lane, wsm); break;
+                case TBE_B200_INT4: pool_bag_by_width<TBE_B200_INT4, IdxT>(p, bag, head, lane, wsm); break;
+                case TBE_B200_FP8: pool_bag_by_width<TBE_B200_FP8, IdxT>(p, bag, head, lane, wsm); break;
+                case TBE_B200_FP16:
+                    if ((m.D & 7) == 0) pool_bag_by_width<TBE_B200_FP16, IdxT>(p, bag, head, lane, wsm);
+                    else done = false;
+                    break;
+                case TBE_B200_FP32: pool_bag_by_width<TBE_B200_FP32, IdxT>(p, bag, head, lane, wsm); break;
+                default: done = false; break;
             }
-            if (!done)
-                pool_bag_bytewise<IdxT>(indices + start, p.pw ? p.pw + start : nullptr, p.error_flag, bag.table, bag.stride,
-                                        L, m.D, bag.seg, bag.mean_mul, m.ty, p.out_ty, p.fp8_shift, p.fp8_mult, lane);
         }
+        if (!done)
+            pool_bag_bytewise<IdxT>(indices + start, p.pw ? p.pw + start : nullptr, p.error_flag, bag.table, bag.stride, L,
+                                    m.D, bag.seg, bag.mean_mul, m.ty, p.out_ty, p.fp8_shift, p.fp8_mult, lane);
         start = end;
-        if (++b == p.B) {
+    }
+}
+
+template <int TY, typename IdxT, bool WEIGHTED>
+__device__ __forceinline__ void pool_run_fast_by_width(const LookupParams& p, const TableMeta& m, int64_t i0, int64_t i1,
+                                                       int64_t b, int lane, uint32_t wsm)
+{
+    const int nunits = m.D / 16;
+    if (nunits <= 2) pool_run_fast<TY, 2, IdxT, WEIGHTED>(p, m, i0, i1, b, lane, wsm);
+    else if (nunits <= 4) pool_run_fast<TY, 4, IdxT, WEIGHTED>(p, m, i0, i1, b, lane, wsm);
+    else if (nunits <= 8) pool_run_fast<TY, 8, IdxT, WEIGHTED>(p, m, i0, i1, b, lane, wsm);
+    else if (nunits <= 16) pool_run_fast<TY, 16, IdxT, WEIGHTED>(p, m, i0, i1, b, lane, wsm);
+    else pool_run_fast<TY, 32, IdxT, WEIGHTED>(p, m, i0, i1, b, lane, wsm);
+}
+
+// ---- kernels -----------------------------------------------------------------
+
+constexpr int kWarpsPerBlock = 4;
+constexpr int kMinBlocksPerSM = 8;   // 32 resident warps per SM: 64 registers and 5 KB of staging memory per warp
+
+// Persistent grid.  The T*B bags (bag i = t*B + b) are cut into one contiguous span per warp, so a warp
+// walks `offsets`, `indices` and the per-sample weights front to back.  A span is processed as runs of
+// consecutive bags of one table: the table's description is read once per run and the run is handed to
+// the code specialised for its row shape.
+template <typename IdxT, int MINB>
+__global__ void __launch_bounds__(kWarpsPerBlock* kWarp, MINB)
+tbe_pooled_kernel(const LookupParams p)
+{
+    __shared__ __align__(16) uint8_t smem[kWarpsPerBlock * kWarpSmemBytes];
+    const int lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5;
+    const uint32_t wsm = smem_u32(smem) + warp * kWarpSmemBytes;
+    const int64_t nw = static_cast<int64_t>(gridDim.x) * kWarpsPerBlock;
+    const int64_t gw = static_cast<int64_t>(blockIdx.x) * kWarpsPerBlock + warp;
+    const int64_t span_lo = p.num_bags / nw * gw + min(gw, p.num_bags % nw);
+    const int64_t span_hi = span_lo + p.num_bags / nw + (gw < p.num_bags % nw ? 1 : 0);
+    if (span_lo >= span_hi) return;
+
+    int t;
+    int64_t b;
+    if (p.B32) {
+        t = static_cast<int>(static_cast<uint32_t>(span_lo) / p.B32);
+        b = static_cast<uint32_t>(span_lo) - static_cast<uint32_t>(t) * p.B32;
+    } else {
+        t = static_cast<int>(span_lo / p.B);
+        b = span_lo - static_cast<int64_t>(t) * p.B;
+    }
+    const bool weighted = p.pw != nullptr;
+
+    for (int64_t i = span_lo; i < span_hi;) {
+        const int64_t run_end = min(span_hi, i + (p.B - b));   // the bags left in table t, or in the span
+        const TableMeta m = load_meta(p, t);
+        if (m.D > 0) {
+            const bool fast = m.rows_aligned && (m.D & 15) == 0 && m.D <= 512 && m.stride < (1ll << 32) &&
+                              (m.ty == TBE_B200_INT8 || m.ty == TBE_B200_INT4);
+            if (fast) {
+                if (m.ty == TBE_B200_INT8) {
+                    if (weighted) pool_run_fast_by_width<TBE_B200_INT8, IdxT, true>(p, m, i, run_end, b, lane, wsm);
+                    else pool_run_fast_by_width<TBE_B200_INT8, IdxT, false>(p, m, i, run_end, b, lane, wsm);
+                } else {
+                    if (weighted) pool_run_fast_by_width<TBE_B200_INT4, IdxT, true>(p, m, i, run_end, b, lane, wsm);
+                    else pool_run_fast_by_width<TBE_B200_INT4, IdxT, false>(p, m, i, run_end, b, lane, wsm);
+                }
+            } else {
+                pool_run_general<IdxT>(p, m, i, run_end, b, lane, wsm);
+            }
+        }
+        b += run_end - i;
+        i = run_end;
+        if (b == p.B) {
             b = 0;
             ++t;
-            if (i + 1 < span_hi) m = load_meta(p, t);
         }
     }
 }
@@ -819,18 +1141,6 @@ tbe_nobag_kernel(const LookupParams p, int64_t num_indices, int max_D)
     for (int e = lane; e < D; e += kWarp)
         store_scalar(seg, e, decode_elem(row, ty, e, scale, bias, p.fp8_shift, p.fp8_mult), p.out_ty);
     for (int e = D + lane; e < max_D; e += kWarp) store_scalar(seg, e, 0.0f, p.out_ty);
-}
-
-// Occupancy variant of the pooled kernel: 10 blocks per SM by default; TBE_B200_BLOCKS_PER_SM=8 selects the
-// build with 64 registers per thread (read once per process; a tuning aid, same results either way).
-int occupancy_variant()
-{
-    static int v = 0;
-    if (v == 0) {
-        const char* e = getenv("TBE_B200_BLOCKS_PER_SM");
-        v = (e && atoi(e) == 8) ? 8 : kMinBlocksPerSM;
-    }
-    return v;
 }
 
 template <typename IdxT, int MINB>
@@ -893,6 +1203,7 @@ extern "C" int tbe_b200_int_nbit_lookup(const tbe_b200_lookup_args* a, tbe_b200_
     p.error_flag = a->error_flag;
     p.B = a->B;
     p.num_bags = static_cast<int64_t>(a->T) * a->B;
+    p.num_indices = a->num_indices;
     p.out_stride = a->output_stride;
     p.rows_per_dest = a->rows_per_dest;
     p.T = a->T;
@@ -918,7 +1229,5 @@ extern "C" int tbe_b200_int_nbit_lookup(const tbe_b200_lookup_args* a, tbe_b200_
         return check_launch("tbe_nobag_kernel");
     }
     if (p.num_bags == 0) return TBE_B200_OK;
-    if (occupancy_variant() == 8)
-        return a->index_bits == 32 ? launch_pooled<int32_t, 8>(p, s) : launch_pooled<int64_t, 8>(p, s);
     return a->index_bits == 32 ? launch_pooled<int32_t, kMinBlocksPerSM>(p, s) : launch_pooled<int64_t, kMinBlocksPerSM>(p, s);
 }

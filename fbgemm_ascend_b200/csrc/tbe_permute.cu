@@ -30,6 +30,8 @@ struct PermuteParams {
     int64_t total_D;
     int64_t in_stride;        // bytes
     int64_t out_stride;       // bytes
+    int64_t blk_cols;         // source columns per block (total_D when the source is one matrix)
+    int64_t blk_stride;       // bytes between consecutive source blocks
     int32_t T;
     int32_t esz;
     bool vec_ok;              // bases and strides are 16-byte aligned
@@ -62,9 +64,13 @@ __global__ void __launch_bounds__(kThreads) permute_pooled_embs_kernel(const Per
     const int64_t pi = __ldg(p.perm + i);
     const bool pi_ok = pi >= 0 && pi < p.T;
     const int64_t src_c0 = pi_ok ? __ldg(p.off + pi) + (c0 - seg_lo) : 0;
+    // Source column c lives in block c / blk_cols at column c % blk_cols.
+    const int64_t blk0 = src_c0 / p.blk_cols;
+    const int64_t in_blk0 = src_c0 - blk0 * p.blk_cols;
 
-    if (p.vec_ok && pi_ok && c0 + ve <= seg_hi && c0 + ve <= p.total_D && ((src_c0 * p.esz) & 15) == 0) {
-        const char* src = p.in + row0 * p.in_stride + src_c0 * p.esz;
+    if (p.vec_ok && pi_ok && c0 + ve <= seg_hi && c0 + ve <= p.total_D && ((in_blk0 * p.esz) & 15) == 0 &&
+        in_blk0 + ve <= p.blk_cols) {
+        const char* src = p.in + blk0 * p.blk_stride + row0 * p.in_stride + in_blk0 * p.esz;
         char* dst = p.out + row0 * p.out_stride + c0 * p.esz;
         uint4 v[kRows];
 #pragma unroll
@@ -87,7 +93,8 @@ __global__ void __launch_bounds__(kThreads) permute_pooled_embs_kernel(const Per
         }
         const int64_t sc = __ldg(p.off + q) + (c - __ldg(p.inv_off + i));
         for (int r = 0; r < nrows; ++r) {
-            const char* s = p.in + (row0 + r) * p.in_stride + sc * p.esz;
+            const int64_t sb = sc / p.blk_cols;
+            const char* s = p.in + sb * p.blk_stride + (row0 + r) * p.in_stride + (sc - sb * p.blk_cols) * p.esz;
             char* d = p.out + (row0 + r) * p.out_stride + c * p.esz;
             if (p.esz == 4) *reinterpret_cast<uint32_t*>(d) = *reinterpret_cast<const uint32_t*>(s);
             else *reinterpret_cast<uint16_t*>(d) = *reinterpret_cast<const uint16_t*>(s);
@@ -98,10 +105,11 @@ __global__ void __launch_bounds__(kThreads) permute_pooled_embs_kernel(const Per
 }  // namespace
 }  // namespace tbe
 
-extern "C" int tbe_b200_permute_pooled_embs(const void* pooled_embs, int64_t B, int64_t total_D, int32_t elem_bytes,
-                                            int64_t in_stride, int64_t out_stride, const int64_t* offset_dim_list,
-                                            const int64_t* permute_list, const int64_t* inv_offset_dim_list, int32_t T,
-                                            void* output, int32_t* error_flag, tbe_b200_stream_t stream)
+extern "C" int tbe_b200_permute_pooled_embs_blocked(const void* pooled_embs, int64_t B, int64_t total_D, int32_t elem_bytes,
+                                                    int64_t in_stride, int64_t out_stride, int64_t block_cols,
+                                                    int64_t block_stride, const int64_t* offset_dim_list,
+                                                    const int64_t* permute_list, const int64_t* inv_offset_dim_list,
+                                                    int32_t T, void* output, int32_t* error_flag, tbe_b200_stream_t stream)
 {
     using namespace tbe;
     if (elem_bytes != 2 && elem_bytes != 4)
@@ -111,8 +119,9 @@ extern "C" int tbe_b200_permute_pooled_embs(const void* pooled_embs, int64_t B, 
     if (B == 0 || total_D == 0) return TBE_B200_OK;
     if (!pooled_embs || !output || !offset_dim_list || !permute_list || !inv_offset_dim_list)
         return fail(TBE_B200_ERR_INVALID_ARGUMENT, "permute_pooled_embs: a required pointer is NULL");
-    if (in_stride < total_D || out_stride < total_D)
-        return fail(TBE_B200_ERR_INVALID_ARGUMENT, "permute_pooled_embs: row stride smaller than total_D");
+    if (block_cols <= 0 || block_cols > total_D) block_cols = total_D;
+    if (in_stride < block_cols || out_stride < total_D)
+        return fail(TBE_B200_ERR_INVALID_ARGUMENT, "permute_pooled_embs: row stride smaller than the row width");
 
     PermuteParams p;
     p.in = static_cast<const char*>(pooled_embs);
@@ -125,10 +134,13 @@ extern "C" int tbe_b200_permute_pooled_embs(const void* pooled_embs, int64_t B, 
     p.total_D = total_D;
     p.in_stride = in_stride * elem_bytes;
     p.out_stride = out_stride * elem_bytes;
+    p.blk_cols = block_cols;
+    p.blk_stride = block_stride * elem_bytes;
     p.T = T;
     p.esz = elem_bytes;
     p.vec_ok = ((reinterpret_cast<uintptr_t>(pooled_embs) | reinterpret_cast<uintptr_t>(output) |
-                 static_cast<uint64_t>(p.in_stride) | static_cast<uint64_t>(p.out_stride)) & 15) == 0;
+                 static_cast<uint64_t>(p.in_stride) | static_cast<uint64_t>(p.out_stride) |
+                 static_cast<uint64_t>(p.blk_stride)) & 15) == 0;
 
     const int ve = 16 / elem_bytes;
     const int64_t nvec = (total_D + ve - 1) / ve;
@@ -150,4 +162,14 @@ extern "C" int tbe_b200_permute_pooled_embs(const void* pooled_embs, int64_t B, 
         permute_pooled_embs_kernel<<<dim3(static_cast<unsigned>(gx), static_cast<unsigned>(this_gy)), kThreads, 0, s>>>(q);
     }
     return check_launch("permute_pooled_embs_kernel");
+}
+
+extern "C" int tbe_b200_permute_pooled_embs(const void* pooled_embs, int64_t B, int64_t total_D, int32_t elem_bytes,
+                                            int64_t in_stride, int64_t out_stride, const int64_t* offset_dim_list,
+                                            const int64_t* permute_list, const int64_t* inv_offset_dim_list, int32_t T,
+                                            void* output, int32_t* error_flag, tbe_b200_stream_t stream)
+{
+    return tbe_b200_permute_pooled_embs_blocked(pooled_embs, B, total_D, elem_bytes, in_stride, out_stride, total_D, 0,
+                                                offset_dim_list, permute_list, inv_offset_dim_list, T, output, error_flag,
+                                                stream);
 }

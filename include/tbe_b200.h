@@ -161,6 +161,19 @@ int tbe_b200_permute_pooled_embs(const void* pooled_embs, int64_t B, int64_t tot
                                  const int64_t* permute_list, const int64_t* inv_offset_dim_list, int32_t T,
                                  void* output, int32_t* error_flag, tbe_b200_stream_t stream);
 
+/* The same permutation over a source that is held as consecutive column blocks:
+ * source column c is read from
+ *   pooled_embs + (c / block_cols) * block_stride + row * in_stride + c % block_cols
+ * (elements).  This is the layout an all-to-all of pooled rows leaves behind (one
+ * [B, block_cols] block per sending rank), so the exchange buffer is permuted into
+ * feature order without first being concatenated.  No counterpart in the reference,
+ * which has no multi-device code. */
+int tbe_b200_permute_pooled_embs_blocked(const void* pooled_embs, int64_t B, int64_t total_D, int32_t elem_bytes,
+                                         int64_t in_stride, int64_t out_stride, int64_t block_cols,
+                                         int64_t block_stride, const int64_t* offset_dim_list,
+                                         const int64_t* permute_list, const int64_t* inv_offset_dim_list, int32_t T,
+                                         void* output, int32_t* error_flag, tbe_b200_stream_t stream);
+
 /* Message of the last failure on the calling thread ("" if none).  Host pointer,
  * valid until the next failing call on the same thread. */
 const char* tbe_b200_last_error(void);

@@ -1,0 +1,128 @@
+"""Table-wise sharding plumbing on CPU ranks (gloo, world size 2): ownership, the exchange and the
+permute lists.  The CUDA operators are replaced by the CPU oracle through the injectable hooks of
+TableWiseShardedLookup, so this runs without a GPU; the GPU data paths are covered by
+tests/test_sharded_gpu.py."""
+import os
+import socket
+import traceback
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+import oracle as O
+from helpers import make_case
+
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    return port
+
+
+def test_shard_plan_lists():
+    from fbgemm_ascend_b200.sharded import ShardPlan
+    dims = [8, 16, 8, 16]
+    plan = ShardPlan(world=2, rank=1, dims=dims, feature_order=[3, 0, 2, 1], global_batch=8)
+    assert plan.tables_of(0) == [0, 2] and plan.local_tables == [1, 3]
+    assert plan.exchanged_order == [0, 2, 1, 3]
+    off, perm, inv_off, inv_perm = plan.permute_lists()
+    assert off == [0, 8, 16, 32, 48]
+    assert perm == [3, 0, 1, 2]                  # feature 3 sits at exchanged position 3, feature 0 at 0, ...
+    assert inv_off == [0, 16, 24, 32, 48]
+    assert [perm[i] for i in inv_perm] == [0, 1, 2, 3]
+    assert plan.local_final_cols() == [32, 0]    # table 1 is last (after 16 + 8 + 8), table 3 first
+    assert plan.local_batch == 4 and plan.total_D == 48
+    with pytest.raises(ValueError):
+        ShardPlan(world=2, rank=0, dims=dims, feature_order=[0, 1, 2, 2], global_batch=8)
+    with pytest.raises(ValueError):
+        ShardPlan(world=2, rank=0, dims=dims, feature_order=[0, 1, 2, 3], global_batch=7)
+
+
+def _global_case():
+    rng = np.random.default_rng(11)
+    dims = [32, 64, 32, 16, 16, 16, 48, 32]     # both ranks hold 128 columns
+    tys = [O.INT8, O.INT4, O.FP16, O.INT8, O.INT8, O.INT4, O.FP16, O.INT8]
+    c = make_case(rng, tys, dims, [200] * 8, 12, [9] * 8, np.int64)
+    order = [5, 2, 7, 0, 3, 6, 1, 4]
+    return c, dims, tys, order
+
+
+def _rank_main(rank, world, port, fail, q):
+    try:
+        os.environ["MASTER_ADDR"] = "127.0.0.1"
+        os.environ["MASTER_PORT"] = str(port)
+        import datetime
+        dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=20))
+        from fbgemm_ascend_b200.sharded import ShardPlan, TableWiseShardedLookup
+        c, dims, tys, order = _global_case()
+        B = c.B
+        plan = ShardPlan(world=world, rank=rank, dims=dims, feature_order=order, global_batch=B)
+        mine = plan.local_tables
+        # the local shard: this rank's tables, and the global batch's bags of those tables
+        offs = c.offsets
+        l_tabs, l_idx, l_lens = [], [], []
+        for t in mine:
+            rb = O.row_bytes(tys[t], dims[t])
+            start = int(c.weights_offsets[t])
+            l_tabs.append(c.dev_weights[start:start + 200 * rb].reshape(200, rb))
+            l_idx.append(c.indices[offs[t * B]:offs[(t + 1) * B]])
+            l_lens.append(np.diff(offs[t * B:(t + 1) * B + 1]))
+        dev, wo, wt, do = O.concat_tables(l_tabs, [tys[t] for t in mine], [dims[t] for t in mine])
+        idx = np.concatenate(l_idx)
+        loffs = np.concatenate([[0], np.cumsum(np.concatenate(l_lens))]).astype(np.int64)
+
+        def lookup_fn(i, o, w):
+            return torch.from_numpy(O.tbe_lookup(dev, wo, wt, do, i.numpy(), o.numpy(), O.SUM, None, O.FP16))
+
+        def permute_fn(blocks, off, perm, inv_off, out):
+            cat = torch.cat([blocks[r] for r in range(blocks.shape[0])], dim=1).numpy()
+            out.copy_(torch.from_numpy(O.permute_pooled_embs(cat, off.numpy(), perm.numpy(), inv_off.numpy())))
+            return out
+
+        sh = TableWiseShardedLookup(plan, tables=None, group=None, exchange="nccl", lookup_fn=lookup_fn,
+                                    permute_fn=permute_fn, device=torch.device("cpu"))
+        if fail and rank == 1:
+            raise RuntimeError("injected failure before the exchange")
+        got = sh(torch.from_numpy(idx), torch.from_numpy(loffs)).numpy()
+        # reference: everything on one process
+        full = O.tbe_lookup(c.dev_weights, c.weights_offsets, c.weights_tys, c.D_offsets, c.indices, c.offsets, O.SUM, None, O.FP16)
+        goff = np.concatenate([[0], np.cumsum(dims)])
+        want = np.concatenate([full[:, goff[t]:goff[t + 1]] for t in order], axis=1)[rank * (B // world):(rank + 1) * (B // world)]
+        q.put((rank, bool(np.array_equal(got.view(np.uint16), want.view(np.uint16))), ""))
+        dist.destroy_process_group()
+    except Exception as e:   # report instead of hanging the parent
+        q.put((rank, False, f"{type(e).__name__}: {e}\n{traceback.format_exc()[-600:]}"))
+
+
+def _run(world, fail):
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_rank_main, args=(r, world, port, fail, q)) for r in range(world)]
+    for pr in procs:
+        pr.start()
+    res = [q.get(timeout=120) for _ in range(world)]
+    for pr in procs:
+        pr.join(timeout=60)
+        if pr.is_alive():
+            pr.kill()
+    return sorted(res)
+
+
+def test_two_rank_exchange_and_permute_bit_exact():
+    res = _run(2, fail=False)
+    assert all(ok for _, ok, _ in res), res
+
+
+def test_rank_failure_before_exchange_surfaces_on_peer():
+    """A rank that raises before the collective must not leave its peer hanging: the peer's exchange
+    ends with an error (connection closed or the process-group timeout)."""
+    res = _run(2, fail=True)
+    assert res[1][1] is False and "injected failure" in res[1][2]
+    assert res[0][1] is False and res[0][2] != ""

@@ -1,0 +1,96 @@
+"""The sharded data paths on real GPUs.  World size 1 runs anywhere; the 2-rank cases need two GPUs
+and are skipped otherwise.  Both exchange paths must give bit-identical results, equal to pooling every
+table on one device and permuting with the public operator."""
+import os
+import socket
+import traceback
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    return port
+
+
+def _rank_main(rank, world, port, q):
+    try:
+        os.environ["MASTER_ADDR"] = "127.0.0.1"
+        os.environ["MASTER_PORT"] = str(port)
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+        torch.cuda.set_device(rank)
+        dev = torch.device("cuda", rank)
+        import datetime
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev, timeout=datetime.timedelta(seconds=120))
+        import fbgemm_ascend_b200  # noqa: F401
+        from fbgemm_ascend_b200 import workloads as W
+        from fbgemm_ascend_b200.sharded import ShardPlan, TableWiseShardedLookup
+        from fbgemm_ascend_b200.modules import PermutePooledEmbeddings
+
+        ws = W.spec("c4", scale_E=0.001, scale_B=1.0 / 64, tables=6)     # 6 tables per rank, 12000 rows, B = 1024
+        T_glob = ws.T * world
+        order = list(np.random.default_rng(3).permutation(T_glob))
+        plan = ShardPlan(world=world, rank=rank, dims=[128] * T_glob, feature_order=[int(x) for x in order], global_batch=ws.B)
+        tables = W.build_tables(ws, dev, table_seed_offset=rank)
+        batch = W.make_batch(ws, dev, batch_seed=0, table_ids=plan.local_tables)
+        pooled = tables.forward(batch.indices, batch.offsets, None)           # [B, 6*128] local tables, global batch
+        # reference: gather every rank's pooled block, order the tables by global id, permute with the operator
+        gathered = [torch.empty_like(pooled) for _ in range(world)]
+        dist.all_gather(gathered, pooled)
+        per_table = {}
+        for r in range(world):
+            for j, t in enumerate(plan.tables_of(r)):
+                per_table[t] = gathered[r][:, j * 128:(j + 1) * 128]
+        cat = torch.cat([per_table[t] for t in range(T_glob)], dim=1)
+        want = PermutePooledEmbeddings([128] * T_glob, [int(x) for x in order], device=dev)(cat)
+        want = want[rank * plan.local_batch:(rank + 1) * plan.local_batch]
+        ok = {}
+        for mode in ("nccl", "direct"):
+            sh = TableWiseShardedLookup(plan, tables, group=dist.group.WORLD, exchange=mode, device=dev)
+            for _ in range(3):    # the direct path alternates between two peer-visible buffers
+                got = sh(batch.indices, batch.offsets, None)
+            torch.cuda.synchronize()
+            ok[mode] = bool(torch.equal(got, want))
+        q.put((rank, ok, ""))
+        dist.barrier()
+        dist.destroy_process_group()
+    except Exception as e:
+        q.put((rank, {}, f"{type(e).__name__}: {e}\n{traceback.format_exc()[-800:]}"))
+
+
+def _run(world):
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_rank_main, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    res = [q.get(timeout=300) for _ in range(world)]
+    for p in procs:
+        p.join(timeout=60)
+        if p.is_alive():
+            p.kill()
+    return sorted(res, key=lambda x: x[0])
+
+
+def test_world_one_both_paths():
+    res = _run(1)
+    assert res[0][2] == "", res[0][2]
+    assert res[0][1] == {"nccl": True, "direct": True}, res
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_two_ranks_both_paths_bit_exact():
+    res = _run(2)
+    for rank, ok, err in res:
+        assert err == "", err
+        assert ok == {"nccl": True, "direct": True}, res
