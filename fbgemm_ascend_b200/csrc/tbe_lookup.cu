@@ -52,6 +52,7 @@ struct LookupParams {
     int64_t num_indices;
     int64_t out_stride;
     int64_t rows_per_dest;
+    int64_t span;        // bags per warp
     int32_t T;
     uint32_t B32;        // B when T*B < 2^32, else 0
     int32_t pooling_mode;
@@ -221,8 +222,7 @@ __device__ __forceinline__ void add_pair_t(float& a0, float& a1, uint32_t pair, 
 constexpr int kChunkBytes = 2048;
 constexpr int kMaxPasses = 8;
 constexpr int kSideBytes = 2 * kMaxPasses * kWarp * 4;
-constexpr int kNextBytes = kWarp * 8 + kWarp * 4 + 16;   // next bag: 32 indices, 32 weights, end offset
-constexpr int kWarpSmemBytes = 2 * kChunkBytes + kSideBytes + kNextBytes;
+constexpr int kWarpSmemBytes = 2 * kChunkBytes + kSideBytes;
 
 struct LaneCtx {
     int unit;        // 16-slot unit handled by this lane in the current block
@@ -739,245 +739,403 @@ __device__ __noinline__ void pool_bag_bytewise(const IdxT* indices, const float*
     }
 }
 
-// The common INT8 / INT4 shape, written for the fewest instructions per row and the fewest exposed
-// latencies per bag.  It handles a run of consecutive bags of ONE table, so everything that depends
-// only on the table or on the lane is computed once per run: D a multiple of 16 and at most 512 means a
-// row is one block of LPR units and the header lane always takes the row's tail; the lane's byte offset
-// into a row, the tail position, the staging addresses and the output position of the lane's finished
-// elements are all loop constants.
-//   * A row address is one 32x32->64-bit multiply-add.  A row that is not to be added (index -1, or past
-//     the end of the bag) is a zero-fill copy whose address is never dereferenced; zero codes with a zero
-//     header add nothing, so no weight or predicate is needed when the rows are consumed.
-//   * The pass loops are free of divergent branches: every lane issues both copies of a pass (its 16 or
-//     8 bytes and the row's tail word; lanes with nothing to fetch copy zero bytes) and reads both back.
-//   * A round requests every row it covers (up to 32) before it consumes any, so all the rows of a
-//     typical bag are in flight together; while the warp waits for them, the indices, weights and end
-//     offset of the NEXT bag are already being loaded (their addresses only need this bag's end).
-//   * The two pass loops are rolled on purpose: one copy of each body keeps the hot code within the
-//     instruction cache.
-template <int TY, int LPR, typename IdxT, bool WEIGHTED>
-__device__ __forceinline__ void pool_run_fast(const LookupParams& p, const TableMeta& m, int64_t i0, int64_t i1, int64_t b,
-                                              int lane, uint32_t wsm)
+// ---- the common shapes: rows staged in shared memory by bulk copies, groups of lanes --------
+//
+// One bulk asynchronous copy (cp.async.bulk, executed by the copy engine of the SM) moves a whole row
+// from global to shared memory; its completion is counted on an mbarrier.  Every lane of a warp issues
+// the copy of a different row, so up to 32 rows per warp are in flight with one instruction and no
+// register holds data that is still on its way.  Source, destination and size are multiples of 16
+// bytes by construction (aligned tables, padded row stride).
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count)
 {
-    static_assert(TY == TBE_B200_INT8 || TY == TBE_B200_INT4, "header types only");
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar)
+{
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect(uint32_t bar, uint32_t bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void bulk_copy_row(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar)
+{
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(src),
+                 "r"(bytes), "r"(bar)
+                 : "memory");
+}
+// Orders this thread's earlier shared-memory accesses before its later asynchronous copies.
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+// Waits for the phase with the given parity.  The wait is bounded: false after kWaitTries polls.
+constexpr int kWaitTries = 1 << 22;
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity)
+{
+    for (int t = 0; t < kWaitTries; ++t) {
+        uint32_t done;
+        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                     : "=r"(done)
+                     : "r"(bar), "r"(parity)
+                     : "memory");
+        if (done) return true;
+    }
+    return false;
+}
+
+// Output address of element 0 of bag `b` of the table at column `col`, when the result is scattered
+// over per-destination buffers (bag b belongs to destination b / rows_per_dest).
+__device__ __forceinline__ char* dest_segment(const LookupParams& p, int64_t b, int64_t col, int esz)
+{
+    int64_t which, rem;
+    if (p.B32) {
+        const uint32_t w = static_cast<uint32_t>(b) / static_cast<uint32_t>(p.rows_per_dest);
+        which = w;
+        rem = static_cast<uint32_t>(b) - w * static_cast<uint32_t>(p.rows_per_dest);
+    } else {
+        which = b / p.rows_per_dest;
+        rem = b - which * p.rows_per_dest;
+    }
+    return static_cast<char*>(p.dests[which]) + (rem * p.out_stride + col) * esz;
+}
+
+constexpr int kStageBytes = kWarpSmemBytes;   // row slots of one warp
+
+// A run of consecutive bags of ONE table whose rows are D = 16 * n <= 512 elements, 16-byte aligned.
+// LPR lanes share a row, 16 elements per lane, so a warp has G = 32 / LPR lane groups, and every group
+// walks its OWN range of the index array:
+//   * normally the groups pool G consecutive bags side by side.  Nothing is exchanged between lanes when
+//     a bag is finished -- a lane simply stores its 16 elements -- and all the per-bag work (offsets,
+//     lengths, addresses, conversion, stores) is done for G bags by one instruction stream;
+//   * when the G bags differ too much in length (or fewer than G are left), the warp takes a single bag
+//     and splits its rows over the groups instead; the groups' partial sums are then combined with a
+//     reduce-scatter over shuffles.  Both forms share the row loop.
+// The row loop works in rounds of R rows per group (R * G <= 32 rows, as many as the warp's staging
+// memory holds).  Lane k < R of a group reads the index of the group's k-th row of the round and issues
+// that row's bulk copy into slot k*G + g (a lane whose row is not to be added -- index -1, or past the
+// group's range -- clears the slot's header, or the whole slot for a type without header, instead).
+// When the round's rows have landed the group reads them back, one per pass: 16 (INT4: 8) bytes per
+// lane, the header word by broadcast, and for INT8/INT4 the row's last 4 / 8 elements, which the lane
+// that owns the header chunk takes into the slots the header leaves free.  Interleaving the slots by
+// group keeps the G header words of a pass in different banks.  The indices of a round are requested
+// one round ahead, so only the first index load of a step is exposed.  (Two rounds of rows in flight per
+// warp, half the rows each, measured slower: the kernel is bound by instruction issue, and shorter
+// rounds mean more per-round work.)
+// FOLD (INT8, unweighted, 16-bit output): the subtraction of the magic constant that turns a code into
+// an fp16 value is skipped, (1024 + q) * scale is accumulated, and 1024 * sum(scale) is removed again at
+// least every 32 rows, which keeps the partial sums small enough for the extra term not to cost
+// precision that a 16-bit result could show.
+// Returns false when a wait for staged rows ran out (reported through the error flag, bit 1).
+template <int TY, int LPR, typename IdxT, bool WEIGHTED, bool FOLD>
+__device__ __noinline__ bool pool_run_staged(const LookupParams& p, const TableMeta& m, int64_t i0, int64_t i1, int64_t b0,
+                                             int lane, uint32_t wsm, uint32_t bar, uint32_t& parity)
+{
+    static_assert(!FOLD || (TY == TBE_B200_INT8 && !WEIGHTED), "the folded form is for unweighted INT8 pooling");
+    constexpr bool kHdr = (TY == TBE_B200_INT8 || TY == TBE_B200_INT4);
     constexpr bool k8 = (TY == TBE_B200_INT8);
-    constexpr int CH = k8 ? 16 : 8;                                    // bytes a lane fetches per row
-    constexpr int RPI = kWarp / LPR;                                   // rows per pass of the warp
-    constexpr int KP = (2 * kChunkBytes) / (kWarp * CH) < kMaxPasses ? (2 * kChunkBytes) / (kWarp * CH) : kMaxPasses;
-    constexpr int UR = (KP < kWarp / RPI) ? KP : (kWarp / RPI);        // passes per round
-    constexpr int RR = UR * RPI;                                       // rows per round (divides 32)
-    constexpr int NF = 16 / RPI;                                       // finished slots per lane after the reduce-scatter
-    constexpr int W = NF >= 4 ? 4 : NF;                                // elements per store
-    constexpr int HS = k8 ? 4 : 8;                                     // slots of the header lane that hold the row's tail
-    static_assert(UR * kWarp * 4 <= kSideBytes && UR * kWarp * CH <= 2 * kChunkBytes, "round does not fit the staging memory");
+    constexpr int CH = (TY == TBE_B200_INT4) ? 8 : 16;                 // bytes per chunk read by a lane
+    constexpr int NCH = (TY == TBE_B200_FP16) ? 2 : (TY == TBE_B200_FP32) ? 4 : 1;   // chunks per lane and row
+    constexpr int EPC = 16 / NCH;                      // elements per chunk
+    constexpr int HS = k8 ? 4 : (TY == TBE_B200_INT4 ? 8 : 0);         // slots of the header lane that hold the row's tail
+    constexpr int G = kWarp / LPR;                     // lane groups = rows per pass of the warp
+    constexpr int LOG_G = G == 1 ? 0 : G == 2 ? 1 : G == 4 ? 2 : 3;
+    constexpr int NF = 16 / G;                         // split form: finished slots per lane after the reduce-scatter
+    constexpr int WS = NF >= 4 ? 4 : NF;               // split form: elements per store
+    static_assert(G <= 8, "at least 4 lanes per row");
     const int k = lane % LPR;
     const int g = lane / LPR;
     const int D = m.D;
-    const bool active = k < D / 16;        // lanes past the row's last unit have nothing to fetch (D < 16 * LPR)
-    const bool head_lane = (k == 0);
+    const int nunits = D / 16;
+    const bool head_lane = kHdr && (k == 0);
+    const bool active = k < nunits;                    // lanes past the row's last unit have nothing to add (D < 16 * LPR)
     const uint32_t stride = static_cast<uint32_t>(m.stride);
-    const uint8_t* lane_base = m.table + k * CH;
-    const uint8_t* tail_base = m.table + (k8 ? D : D / 2);             // elements D-4.. (INT8) / D-8.. (INT4)
-    const uint32_t slot0 = wsm + lane * CH;
-    const uint32_t side0 = wsm + 2 * kChunkBytes + lane * 4;
-    const int full_bytes = active ? CH : 0;
-    const IdxT* offsets = static_cast<const IdxT*>(p.offsets);
+    const uint32_t copy_bytes = static_cast<uint32_t>(row_bytes_of(TY, D, 16));   // the row without its alignment padding
+    const int R = min(LPR, (kStageBytes / static_cast<int>(copy_bytes)) >> LOG_G);   // rows per group and round (>= 1)
+    const uint32_t own_slot = wsm + static_cast<uint32_t>(k * G + g) * copy_bytes;   // the slot this lane fills (k < R)
+    const uint32_t read0 = wsm + static_cast<uint32_t>(g) * copy_bytes + (active ? k * CH : 0);   // pass 0, chunk 0
+    const uint32_t pass_pitch = G * copy_bytes;
+    // INT8/INT4: the extra word of a pass is the row's tail for the header lane and the header for the others.
+    const uint32_t extra0 = wsm + static_cast<uint32_t>(g) * copy_bytes + (head_lane ? (k8 ? D : D / 2) : 0);
+    const IdxT* offs = static_cast<const IdxT*>(p.offsets) + i0;
     const IdxT* indices = static_cast<const IdxT*>(p.indices);
-    const int64_t N = p.num_indices;
+    const int nb = static_cast<int>(i1 - i0);
     const int esz = (p.out_ty == TBE_B200_FP32) ? 4 : 2;
     const int64_t row_bytes = p.out_stride * esz;
-
-    // Where this lane's finished elements go: slot -> element is fixed per lane.  Unit k covers elements
-    // [16k - HS, 16k + 16 - HS); the header lane's first HS slots are the last HS elements of the row.
-    int slot_base = 0;
-    if constexpr (RPI >= 2) slot_base += ((lane >> 4) & 1) ? 8 : 0;
-    if constexpr (RPI >= 4) slot_base += ((lane >> 3) & 1) ? 4 : 0;
-    if constexpr (RPI >= 8) slot_base += ((lane >> 2) & 1) ? 2 : 0;
-    if constexpr (RPI >= 16) slot_base += ((lane >> 1) & 1) ? 1 : 0;
-    int e_first[NF / W];
-#pragma unroll
-    for (int q = 0; q < NF / W; ++q) {
-        const int slot = slot_base + q * W;
-        e_first[q] = (head_lane && slot < HS) ? (D - HS + slot) : (16 * k - HS + slot);
-    }
-    char* out_table = nullptr;             // output address of (row 0, first column of this table)
+    const bool mean = p.pooling_mode == TBE_B200_POOL_MEAN;
+    char* out_run = nullptr;               // output address of (bag b0, first column of this table)
     bool vec_ok = false;
     if (!p.dests) {
-        out_table = static_cast<char*>(p.output) + m.col * esz;
-        vec_ok = ((reinterpret_cast<uintptr_t>(out_table) | static_cast<uint64_t>(row_bytes)) & 15) == 0;
+        out_run = static_cast<char*>(p.output) + m.col * esz + b0 * row_bytes;
+        vec_ok = ((reinterpret_cast<uintptr_t>(out_run) | static_cast<uint64_t>(row_bytes)) & 15) == 0;
     }
-
-    // Staging for the NEXT bag's first 32 indices and weights and its end offset.  They are fetched with
-    // cp.async, not into registers: a register that holds an outstanding load across the whole bag body
-    // gets spilled, and the spill store waits for the load -- which would serialise the two latencies.
-    const uint32_t nx_idx = wsm + 2 * kChunkBytes + kSideBytes + lane * static_cast<int>(sizeof(IdxT));
-    const uint32_t nx_w = wsm + 2 * kChunkBytes + kSideBytes + kWarp * 8 + lane * 4;
-    const uint32_t nx_end = wsm + 2 * kChunkBytes + kSideBytes + kWarp * 12;
-
-    auto request_bag_head = [&](int64_t first, int64_t bag_i) {
-        // indices[first + lane], weights[first + lane] (zero-filled past the end of the arrays), offsets[bag_i + 1]
-        const bool in = first + lane < N;
-        if constexpr (sizeof(IdxT) == 8) cp_async8(nx_idx, indices + (in ? first + lane : 0), in ? 8 : 0);
-        else cp_async4(nx_idx, indices + (in ? first + lane : 0), in ? 4 : 0);
-        if constexpr (WEIGHTED) cp_async4(nx_w, p.pw + (in ? first + lane : 0), in ? 4 : 0);
-        if (lane == 0) {
-            if constexpr (sizeof(IdxT) == 8) cp_async8(nx_end, offsets + bag_i + 1, 8);
-            else cp_async4(nx_end, offsets + bag_i + 1, 4);
-        }
-        cp_async_commit();
+    // Element a slot stands for.  Chunk c = k + (slot / EPC) * nunits of the row holds EPC elements; INT8/INT4
+    // chunks are shifted by the header (unit k covers elements [16k - HS, 16k + 16 - HS)), and the header
+    // lane's first HS slots are the row's last HS elements.
+    auto elem_of = [&](int slot) -> int {
+        if constexpr (kHdr) return (head_lane && slot < HS) ? (D - HS + slot) : (16 * k - HS + slot);
+        else return EPC * (k + (slot / EPC) * nunits) + (slot % EPC);
     };
+    // Split form: which of its 16 slots a lane ends up with.
+    int slot_base = 0;
+    if constexpr (G >= 2) slot_base += ((lane >> 4) & 1) ? 8 : 0;
+    if constexpr (G >= 4) slot_base += ((lane >> 3) & 1) ? 4 : 0;
+    if constexpr (G >= 8) slot_base += ((lane >> 2) & 1) ? 2 : 0;
 
-    int64_t start = static_cast<int64_t>(__ldg(offsets + i0));
-    request_bag_head(start, i0);
+    for (int j = 0; j < nb;) {
+        // Group g looks at bag j + g (an empty one past the end of the run).
+        const int64_t o0 = static_cast<int64_t>(__ldg(offs + min(j + g, nb)));
+        const int64_t o1 = static_cast<int64_t>(__ldg(offs + min(j + g + 1, nb)));
+        const int Lg = static_cast<int>(o1 - o0);
+        int maxL = Lg, sumL = Lg;
+#pragma unroll
+        for (int d = LPR; d < kWarp; d <<= 1) {
+            maxL = max(maxL, __shfl_xor_sync(kFull, maxL, d));
+            sumL += __shfl_xor_sync(kFull, sumL, d);
+        }
+        // Side by side costs max(L) passes; one bag at a time costs about L / G + 4 passes per bag.
+        const int bags_here = min(G, nb - j);
+        const bool split = (G > 1) && (maxL + 2 > (sumL >> LOG_G) + 4 * bags_here);
+        int64_t lo = o0;      // this group's rows are indices[lo .. lo + n)
+        int n = Lg;
+        int maxn = maxL;      // rows of the longest group
+        int Lbag = Lg;        // length of the bag this lane contributes to
+        if (split) {
+            Lbag = __shfl_sync(kFull, Lg, 0);
+            const int64_t start = __shfl_sync(kFull, o0, 0);
+            const int per = (Lbag + G - 1) >> LOG_G;
+            const int a = min(Lbag, g * per);
+            lo = start + a;
+            n = min(Lbag, a + per) - a;
+            maxn = per;
+        }
+        const IdxT* ip = indices + lo + k;
+        const float* wp = WEIGHTED ? p.pw + lo + k : nullptr;
+        const int nrounds = (maxn + R - 1) / R;
 
-    for (int64_t i = i0; i < i1; ++i, ++b) {
-        cp_async_wait<0>();
-        __syncwarp();   // lane 0's copy of the end offset is read by every lane
-        IdxT raw_idx;
-        int64_t end;
-        if constexpr (sizeof(IdxT) == 8) {
-            const uint2 v = lds8(nx_idx);
-            raw_idx = static_cast<IdxT>((static_cast<uint64_t>(v.y) << 32) | v.x);
-            const uint2 e = lds8(nx_end);
-            end = static_cast<int64_t>((static_cast<uint64_t>(e.y) << 32) | e.x);
-        } else {
-            raw_idx = static_cast<IdxT>(lds4(nx_idx));
-            end = static_cast<int64_t>(static_cast<int32_t>(lds4(nx_end)));
-        }
-        float my_w = 1.0f;
-        if constexpr (WEIGHTED) my_w = __uint_as_float(lds4(nx_w));
-        __syncwarp();   // everyone has read the staging words before they are requested again
-        const int L = static_cast<int>(end - start);
-        // The lanes hold the indices of rows [batch0, batch0 + 32) of the bag, narrowed to 32 bits.
-        int batch0 = 0;
-        int32_t my_idx;
-        {
-            const bool bad = (raw_idx < static_cast<IdxT>(-1)) || (sizeof(IdxT) == 8 && static_cast<int64_t>(raw_idx) > 0x7fffffffll);
-            my_idx = (lane < L && !bad) ? static_cast<int32_t>(raw_idx) : -1;
-            if (lane < L && bad && p.error_flag) atomicOr(p.error_flag, 1);
-        }
-        bool head_requested = false;   // the next bag's head goes out right after this bag's first round of rows
+        // Lane k < R of the group takes row r*R + k of round r.  The raw index is kept as loaded and only
+        // looked at when the round is issued, one iteration later, so the load has that long to arrive.
+        auto load_raw = [&](int r, IdxT& raw, float& w) {
+            raw = static_cast<IdxT>(-1);
+            w = 0.0f;
+            if (k < R && r * R + k < n) {
+                raw = __ldg(ip + r * R);
+                if constexpr (WEIGHTED) w = __ldg(wp + r * R);
+            }
+        };
+        // Index narrowed to 32 bits, -1 = nothing to add.
+        auto narrow = [&](IdxT raw) -> int32_t {
+            const bool bad = (raw < static_cast<IdxT>(-1)) || (sizeof(IdxT) == 8 && static_cast<int64_t>(raw) > 0x7fffffffll);
+            if (bad) {
+                if (p.error_flag) atomicOr(p.error_flag, 1);
+                return -1;
+            }
+            return static_cast<int32_t>(raw);
+        };
+        // Starts a round: the copy of this lane's row into its slot, or a cleared slot.
+        auto issue = [&](int32_t idx) {
+            const uint32_t slot = own_slot;
+            const uint32_t sbar = bar;
+            // The reads of the previous round (by every lane) come before the writes of this round.
+            __syncwarp();
+            fence_async_smem();
+            if (idx >= 0) {
+                mbar_arrive_expect(sbar, copy_bytes);
+                bulk_copy_row(slot, m.table + static_cast<uint64_t>(static_cast<uint32_t>(idx)) * stride, copy_bytes, sbar);
+            } else {
+                if (k < R) {
+                    if constexpr (kHdr) {
+                        asm volatile("st.shared.b32 [%0], %1;" ::"r"(slot), "r"(0u) : "memory");
+                    } else {
+                        for (uint32_t o = 0; o < copy_bytes; o += 16)
+                            asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(slot + o), "r"(0u) : "memory");
+                    }
+                }
+                mbar_arrive(sbar);
+            }
+        };
 
         float acc[16];
 #pragma unroll
-        for (int j = 0; j < 16; ++j) acc[j] = 0.0f;
+        for (int s = 0; s < 16; ++s) acc[s] = 0.0f;
         float bias_acc = 0.0f;
+        float scale_acc = 0.0f;   // sum of the row scales since the last fold (FOLD only)
+        int since_fold = 0;
+        (void)scale_acc;
+        (void)since_fold;
 
-        for (int row0 = 0; row0 < L; row0 += RR) {
-            if (row0 >= batch0 + kWarp) {
-                batch0 += kWarp;
-                const BagHead nb = load_batch<IdxT>(indices + start + batch0, WEIGHTED ? p.pw + start + batch0 : nullptr,
-                                                    L - batch0, lane, p.error_flag);
-                my_idx = nb.idx;
-                my_w = nb.w;
-            }
-            const int npass = (min(RR, L - row0) + RPI - 1) / RPI;
-            const int src0 = (row0 - batch0) + g;   // lane holding the index of this group's row in pass 0
-            uint32_t slot = slot0, side = side0;
+        IdxT raw_next;
+        float w_cur = 0.0f, w_next = 0.0f;
+        if (nrounds > 0) {
+            IdxT raw0;
+            load_raw(0, raw0, w_cur);
+            load_raw(1, raw_next, w_next);
+            const int32_t idx0 = narrow(raw0);
+            if (idx0 < 0) w_cur = 0.0f;
+            issue(idx0);
+        }
 #pragma unroll 1
-            for (int u = 0; u < npass; ++u) {
-                const int32_t idx = __shfl_sync(kFull, my_idx, src0 + u * RPI);
-                const bool ok = idx >= 0;
-                const uint64_t off = static_cast<uint64_t>(static_cast<uint32_t>(idx)) * stride;
-                if (k8) cp_async16(slot, lane_base + off, ok ? full_bytes : 0);
-                else cp_async8(slot, lane_base + off, ok ? full_bytes : 0);
-                cp_async4(side, tail_base + off, ok ? 4 : 0);
-                slot += kWarp * CH;
-                side += kWarp * 4;
+        for (int r = 0; r < nrounds; ++r) {
+            if (!mbar_wait(bar, parity)) {
+                if (p.error_flag) atomicOr(p.error_flag, 2);
+                return false;
             }
-            cp_async_commit();
-            if (!head_requested && i + 1 < i1) {
-                // Next bag: its first indices start where this bag ends, so they can be requested now and
-                // arrive while this bag is being pooled.
-                request_bag_head(end, i + 1);
-                if (lane == 0 && end + 4 * kWarp < N) prefetch_l2(indices + end + 4 * kWarp);
-                head_requested = true;
-                cp_async_wait<1>();   // this round's rows are in; the head may still be on its way
-            } else {
-                cp_async_wait<0>();
-            }
-            slot = slot0;
-            side = side0;
-#pragma unroll 1
-            for (int u = 0; u < npass; ++u) {
-                uint32_t words[4] = {0u, 0u, 0u, 0u};
-                if (k8) {
-                    const uint4 v = lds16(slot);
-                    words[0] = v.x; words[1] = v.y; words[2] = v.z; words[3] = v.w;
-                } else {
-                    const uint2 v = lds8(slot);
-                    words[0] = v.x; words[1] = v.y;
-                }
-                const uint32_t tail = lds4(side);
-                slot += kWarp * CH;
-                side += kWarp * 4;
-                // The header is the first word of unit 0; that lane then swaps in the row's tail.
-                const uint32_t hdr = __shfl_sync(kFull, words[0], 0, LPR);
-                words[0] = head_lane ? tail : words[0];
-                const unsigned short scale_h = static_cast<unsigned short>(hdr & 0xffffu);
-                float ws = 0.0f;
-                if constexpr (WEIGHTED) {
-                    const float w = __shfl_sync(kFull, my_w, src0 + u * RPI);
-                    ws = half_bits_to_float(scale_h) * w;
-                    bias_acc = fmaf(half_bits_to_float(hdr >> 16), w, bias_acc);
-                } else {
-                    bias_acc += half_bits_to_float(hdr >> 16);
-                }
-                if (k8) {
+            parity ^= 1u;
+
+            const int cnt = min(R, maxn - r * R);
+            uint32_t rd = read0, ex = extra0;
+#pragma unroll 2
+            for (int u = 0; u < cnt; ++u, rd += pass_pitch, ex += pass_pitch) {
+                float w = 1.0f;
+                if constexpr (WEIGHTED) w = __shfl_sync(kFull, w_cur, u, LPR);
+                if constexpr (kHdr) {
+                    uint32_t words[4] = {0u, 0u, 0u, 0u};
+                    if (k8) {
+                        const uint4 v = lds16(rd);
+                        words[0] = v.x; words[1] = v.y; words[2] = v.z; words[3] = v.w;
+                    } else {
+                        const uint2 v = lds8(rd);
+                        words[0] = v.x; words[1] = v.y;
+                    }
+                    const uint32_t x = lds4(ex);
+                    const uint32_t hdr = head_lane ? words[0] : x;
+                    const uint32_t w0 = head_lane ? x : words[0];
+                    const unsigned short scale_h = static_cast<unsigned short>(hdr & 0xffffu);
+                    float ws = 0.0f;
+                    if constexpr (WEIGHTED) {
+                        ws = half_bits_to_float(scale_h) * w;
+                        bias_acc = fmaf(half_bits_to_float(hdr >> 16), w, bias_acc);
+                    } else {
+                        bias_acc += half_bits_to_float(hdr >> 16);
+                        if constexpr (FOLD) scale_acc += half_bits_to_float(scale_h);
+                    }
+                    if (k8) {
+#pragma unroll
+                        for (int i4 = 0; i4 < 4; ++i4) {
+                            const uint32_t c = (i4 == 0) ? w0 : words[i4];
+                            // bytes 0 and 2, then bytes 1 and 3, placed in the mantissas of half2(1024, 1024)
+                            uint32_t even = (c & 0x00FF00FFu) | 0x64006400u;
+                            uint32_t odd = __byte_perm(c, 0x64646464u, 0x4341);
+                            if constexpr (!FOLD) {
+                                even = codes_to_half2(even, 0x64006400u);
+                                odd = codes_to_half2(odd, 0x64006400u);
+                            }
+                            add_pair_t<WEIGHTED>(acc[4 * i4 + 0], acc[4 * i4 + 2], even, scale_h, ws);
+                            add_pair_t<WEIGHTED>(acc[4 * i4 + 1], acc[4 * i4 + 3], odd, scale_h, ws);
+                        }
+                    } else {
+#pragma unroll
+                        for (int i2 = 0; i2 < 2; ++i2) {
+                            const uint32_t c = (i2 == 0) ? w0 : words[i2];
+                            const uint32_t y = c >> 8;
+                            // nibble pairs (j, j + 4) sit 16 bits apart: 0x6400 | n = 1024 + n; 0x5400 | (n << 4) = 64 + n
+                            const uint32_t p0 = codes_to_half2((c & 0x000F000Fu) | 0x64006400u, 0x64006400u);   // nibbles 0, 4
+                            const uint32_t p1 = codes_to_half2((c & 0x00F000F0u) | 0x54005400u, 0x54005400u);   // nibbles 1, 5
+                            const uint32_t p2 = codes_to_half2((y & 0x000F000Fu) | 0x64006400u, 0x64006400u);   // nibbles 2, 6
+                            const uint32_t p3 = codes_to_half2((y & 0x00F000F0u) | 0x54005400u, 0x54005400u);   // nibbles 3, 7
+                            add_pair_t<WEIGHTED>(acc[8 * i2 + 0], acc[8 * i2 + 4], p0, scale_h, ws);
+                            add_pair_t<WEIGHTED>(acc[8 * i2 + 1], acc[8 * i2 + 5], p1, scale_h, ws);
+                            add_pair_t<WEIGHTED>(acc[8 * i2 + 2], acc[8 * i2 + 6], p2, scale_h, ws);
+                            add_pair_t<WEIGHTED>(acc[8 * i2 + 3], acc[8 * i2 + 7], p3, scale_h, ws);
+                        }
+                    }
+                } else if constexpr (TY == TBE_B200_FP8) {
+                    // byte -> fp32 by bit placement: ((b & 0x7f) << (16 + ebits)) as a float, times 2^(127 - bias),
+                    // sign bit or'ed in (reference: c310/op_kernel/common.h:120-167)
+                    const uint4 v = lds16(rd);
+                    const uint32_t words[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
                     for (int i4 = 0; i4 < 4; ++i4) {
-                        // bytes 0 and 2, then bytes 1 and 3, masked into the mantissas of half2(1024, 1024)
-                        const uint32_t even = codes_to_half2((words[i4] & 0x00FF00FFu) | 0x64006400u, 0x64006400u);
-                        const uint32_t odd = codes_to_half2(((words[i4] >> 8) & 0x00FF00FFu) | 0x64006400u, 0x64006400u);
-                        add_pair_t<WEIGHTED>(acc[4 * i4 + 0], acc[4 * i4 + 2], even, scale_h, ws);
-                        add_pair_t<WEIGHTED>(acc[4 * i4 + 1], acc[4 * i4 + 3], odd, scale_h, ws);
+#pragma unroll
+                        for (int b4 = 0; b4 < 4; ++b4) {
+                            const uint32_t by = (words[i4] >> (8 * b4)) & 0xffu;
+                            const float mag = __uint_as_float((by & 0x7fu) << p.fp8_shift) * p.fp8_mult;
+                            const float val = __uint_as_float(__float_as_uint(mag) | ((by & 0x80u) << 24));
+                            acc[4 * i4 + b4] = fmaf(w, val, acc[4 * i4 + b4]);
+                        }
+                    }
+                } else if constexpr (TY == TBE_B200_FP16) {
+#pragma unroll
+                    for (int c = 0; c < 2; ++c) {
+                        const uint4 v = lds16(rd + c * nunits * 16);
+                        const uint32_t words[4] = {v.x, v.y, v.z, v.w};
+                        // unweighted: value * 1.0 + acc in one mixed FMA
+#pragma unroll
+                        for (int i4 = 0; i4 < 4; ++i4)
+                            add_pair_t<WEIGHTED>(acc[8 * c + 2 * i4], acc[8 * c + 2 * i4 + 1], words[i4], 0x3c00u, w);
                     }
                 } else {
 #pragma unroll
-                    for (int i2 = 0; i2 < 2; ++i2) {
-                        const uint32_t x = words[i2], y = words[i2] >> 8;
-                        const uint32_t p0 = codes_to_half2((x & 0x000F000Fu) | 0x64006400u, 0x64006400u);   // nibbles 0, 4
-                        const uint32_t p1 = codes_to_half2((x & 0x00F000F0u) | 0x54005400u, 0x54005400u);   // nibbles 1, 5
-                        const uint32_t p2 = codes_to_half2((y & 0x000F000Fu) | 0x64006400u, 0x64006400u);   // nibbles 2, 6
-                        const uint32_t p3 = codes_to_half2((y & 0x00F000F0u) | 0x54005400u, 0x54005400u);   // nibbles 3, 7
-                        add_pair_t<WEIGHTED>(acc[8 * i2 + 0], acc[8 * i2 + 4], p0, scale_h, ws);
-                        add_pair_t<WEIGHTED>(acc[8 * i2 + 1], acc[8 * i2 + 5], p1, scale_h, ws);
-                        add_pair_t<WEIGHTED>(acc[8 * i2 + 2], acc[8 * i2 + 6], p2, scale_h, ws);
-                        add_pair_t<WEIGHTED>(acc[8 * i2 + 3], acc[8 * i2 + 7], p3, scale_h, ws);
+                    for (int c = 0; c < 4; ++c) {
+                        const uint4 v = lds16(rd + c * nunits * 16);
+                        acc[4 * c + 0] = fmaf(w, __uint_as_float(v.x), acc[4 * c + 0]);
+                        acc[4 * c + 1] = fmaf(w, __uint_as_float(v.y), acc[4 * c + 1]);
+                        acc[4 * c + 2] = fmaf(w, __uint_as_float(v.z), acc[4 * c + 2]);
+                        acc[4 * c + 3] = fmaf(w, __uint_as_float(v.w), acc[4 * c + 3]);
                     }
                 }
             }
-        }
-
-        // Combine the RPI groups (reduce-scatter over shuffles), add the pooled biases, scale for MEAN, store.
-        if constexpr (RPI >= 2) halve<16>(acc, 16, (lane >> 4) & 1);
-        if constexpr (RPI >= 4) halve<8>(acc, 8, (lane >> 3) & 1);
-        if constexpr (RPI >= 8) halve<4>(acc, 4, (lane >> 2) & 1);
-        if constexpr (RPI >= 16) halve<2>(acc, 2, (lane >> 1) & 1);
+            if constexpr (FOLD) {
+                since_fold += cnt;
+                if (since_fold >= 32) {
 #pragma unroll
-        for (int d = LPR; d < kWarp; d <<= 1) bias_acc += __shfl_xor_sync(kFull, bias_acc, d);
-        const float mean_mul = (p.pooling_mode == TBE_B200_POOL_MEAN && L > 0) ? 1.0f / static_cast<float>(L) : 1.0f;
-        char* seg;
-        bool vec = vec_ok;
-        if (p.dests) {
-            const int64_t which = b / p.rows_per_dest;
-            seg = static_cast<char*>(p.dests[which]) + ((b - which * p.rows_per_dest) * p.out_stride + m.col) * esz;
-            vec = (reinterpret_cast<uintptr_t>(seg) & 15) == 0;
-        } else {
-            seg = out_table + b * row_bytes;
-        }
-        if (active) {
-#pragma unroll
-            for (int q = 0; q < NF / W; ++q) {
-                float v[W];
-#pragma unroll
-                for (int j = 0; j < W; ++j) v[j] = (acc[q * W + j] + bias_acc) * mean_mul;
-                store_out<W>(seg, e_first[q], v, p.out_ty, vec);
+                    for (int s = 0; s < 16; ++s) acc[s] = fmaf(-1024.0f, scale_acc, acc[s]);
+                    scale_acc = 0.0f;
+                    since_fold = 0;
+                }
+            }
+            if (r + 1 < nrounds) {
+                // The next round's rows go out (its indices were requested a round ago), then the request for
+                // the indices of the round after it.
+                const int32_t idx1 = narrow(raw_next);
+                w_cur = (idx1 >= 0) ? w_next : 0.0f;
+                issue(idx1);
+                load_raw(r + 2, raw_next, w_next);
             }
         }
-        if (!head_requested && i + 1 < i1) request_bag_head(end, i + 1);   // an empty bag ran no round
-        start = end;
+        // What is left of the folded offset goes out with the biases.
+        if constexpr (FOLD) bias_acc = fmaf(-1024.0f, scale_acc, bias_acc);
+        const float mean_mul = (mean && Lbag > 0) ? 1.0f / static_cast<float>(Lbag) : 1.0f;
+
+        if (!split) {
+            // Every group stores its own bag: slots [4q, 4q + 4) of a lane are 4 consecutive elements.
+            const int64_t bag = j + g;
+            char* seg = p.dests ? dest_segment(p, b0 + bag, m.col, esz) : out_run + bag * row_bytes;
+            const bool vec = p.dests ? (reinterpret_cast<uintptr_t>(seg) & 15) == 0 : vec_ok;
+            if (active && bag < nb) {
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    float v[4];
+#pragma unroll
+                    for (int s = 0; s < 4; ++s) v[s] = (acc[4 * q + s] + bias_acc) * mean_mul;
+                    store_out<4>(seg, elem_of(4 * q), v, p.out_ty, vec);
+                }
+            }
+            j += G;
+        } else {
+            // One bag over all groups: reduce-scatter the partial sums, add the pooled biases, store.
+            if constexpr (G >= 2) halve<16>(acc, 16, (lane >> 4) & 1);
+            if constexpr (G >= 4) halve<8>(acc, 8, (lane >> 3) & 1);
+            if constexpr (G >= 8) halve<4>(acc, 4, (lane >> 2) & 1);
+            if constexpr (kHdr) {
+#pragma unroll
+                for (int d = LPR; d < kWarp; d <<= 1) bias_acc += __shfl_xor_sync(kFull, bias_acc, d);
+            }
+            char* seg = p.dests ? dest_segment(p, b0 + j, m.col, esz) : out_run + static_cast<int64_t>(j) * row_bytes;
+            const bool vec = p.dests ? (reinterpret_cast<uintptr_t>(seg) & 15) == 0 : vec_ok;
+            if (active) {
+#pragma unroll
+                for (int q = 0; q < NF / WS; ++q) {
+                    float v[WS];
+#pragma unroll
+                    for (int s = 0; s < WS; ++s) v[s] = (acc[q * WS + s] + bias_acc) * mean_mul;
+                    store_out<WS>(seg, elem_of(slot_base + q * WS), v, p.out_ty, vec);
+                }
+            }
+            j += 1;
+        }
     }
+    return true;
 }
 
 // A run of bags of one table through the general per-bag code.
@@ -1033,16 +1191,33 @@ __device__ __forceinline__ void pool_run_general(const LookupParams& p, const Ta
     }
 }
 
-template <int TY, typename IdxT, bool WEIGHTED>
-__device__ __forceinline__ void pool_run_fast_by_width(const LookupParams& p, const TableMeta& m, int64_t i0, int64_t i1,
-                                                       int64_t b, int lane, uint32_t wsm)
+template <int TY, typename IdxT, bool WEIGHTED, bool FOLD>
+__device__ __forceinline__ bool pool_run_staged_by_width(const LookupParams& p, const TableMeta& m, int64_t i0, int64_t i1,
+                                                         int64_t b, int lane, uint32_t wsm, uint32_t bar, uint32_t& parity)
 {
     const int nunits = m.D / 16;
-    if (nunits <= 2) pool_run_fast<TY, 2, IdxT, WEIGHTED>(p, m, i0, i1, b, lane, wsm);
-    else if (nunits <= 4) pool_run_fast<TY, 4, IdxT, WEIGHTED>(p, m, i0, i1, b, lane, wsm);
-    else if (nunits <= 8) pool_run_fast<TY, 8, IdxT, WEIGHTED>(p, m, i0, i1, b, lane, wsm);
-    else if (nunits <= 16) pool_run_fast<TY, 16, IdxT, WEIGHTED>(p, m, i0, i1, b, lane, wsm);
-    else pool_run_fast<TY, 32, IdxT, WEIGHTED>(p, m, i0, i1, b, lane, wsm);
+    if (nunits <= 4) return pool_run_staged<TY, 4, IdxT, WEIGHTED, FOLD>(p, m, i0, i1, b, lane, wsm, bar, parity);
+    if (nunits <= 8) return pool_run_staged<TY, 8, IdxT, WEIGHTED, FOLD>(p, m, i0, i1, b, lane, wsm, bar, parity);
+    if (nunits <= 16) return pool_run_staged<TY, 16, IdxT, WEIGHTED, FOLD>(p, m, i0, i1, b, lane, wsm, bar, parity);
+    return pool_run_staged<TY, 32, IdxT, WEIGHTED, FOLD>(p, m, i0, i1, b, lane, wsm, bar, parity);
+}
+
+template <typename IdxT, bool WEIGHTED>
+__device__ __forceinline__ bool pool_run_staged_by_type(const LookupParams& p, const TableMeta& m, int64_t i0, int64_t i1,
+                                                        int64_t b, int lane, uint32_t wsm, uint32_t bar, uint32_t& parity)
+{
+    switch (m.ty) {
+        case TBE_B200_INT8:
+            if constexpr (!WEIGHTED) {
+                if (p.out_ty != TBE_B200_FP32)
+                    return pool_run_staged_by_width<TBE_B200_INT8, IdxT, false, true>(p, m, i0, i1, b, lane, wsm, bar, parity);
+            }
+            return pool_run_staged_by_width<TBE_B200_INT8, IdxT, WEIGHTED, false>(p, m, i0, i1, b, lane, wsm, bar, parity);
+        case TBE_B200_INT4: return pool_run_staged_by_width<TBE_B200_INT4, IdxT, WEIGHTED, false>(p, m, i0, i1, b, lane, wsm, bar, parity);
+        case TBE_B200_FP8: return pool_run_staged_by_width<TBE_B200_FP8, IdxT, WEIGHTED, false>(p, m, i0, i1, b, lane, wsm, bar, parity);
+        case TBE_B200_FP16: return pool_run_staged_by_width<TBE_B200_FP16, IdxT, WEIGHTED, false>(p, m, i0, i1, b, lane, wsm, bar, parity);
+        default: return pool_run_staged_by_width<TBE_B200_FP32, IdxT, WEIGHTED, false>(p, m, i0, i1, b, lane, wsm, bar, parity);
+    }
 }
 
 // ---- kernels -----------------------------------------------------------------
@@ -1050,23 +1225,28 @@ __device__ __forceinline__ void pool_run_fast_by_width(const LookupParams& p, co
 constexpr int kWarpsPerBlock = 4;
 constexpr int kMinBlocksPerSM = 8;   // 32 resident warps per SM: 64 registers and 5 KB of staging memory per warp
 
-// Persistent grid.  The T*B bags (bag i = t*B + b) are cut into one contiguous span per warp, so a warp
-// walks `offsets`, `indices` and the per-sample weights front to back.  A span is processed as runs of
-// consecutive bags of one table: the table's description is read once per run and the run is handed to
-// the code specialised for its row shape.
+// The T*B bags (bag i = t*B + b) are cut into spans of `span` consecutive bags, one span per warp, so a
+// warp walks `offsets`, `indices` and the per-sample weights front to back.  A span is processed as runs
+// of consecutive bags of one table: the table's description is read once per run and the run is handed
+// to the code specialised for its row shape.
 template <typename IdxT, int MINB>
 __global__ void __launch_bounds__(kWarpsPerBlock* kWarp, MINB)
-tbe_pooled_kernel(const LookupParams p)
+tbe_pooled_kernel(const __grid_constant__ LookupParams p)
 {
-    __shared__ __align__(16) uint8_t smem[kWarpsPerBlock * kWarpSmemBytes];
+    __shared__ __align__(128) uint8_t smem[kWarpsPerBlock * kWarpSmemBytes];
+    __shared__ __align__(8) uint64_t bars[kWarpsPerBlock];
     const int lane = threadIdx.x & 31;
     const int warp = threadIdx.x >> 5;
     const uint32_t wsm = smem_u32(smem) + warp * kWarpSmemBytes;
-    const int64_t nw = static_cast<int64_t>(gridDim.x) * kWarpsPerBlock;
+    const uint32_t bar = smem_u32(&bars[warp]);
     const int64_t gw = static_cast<int64_t>(blockIdx.x) * kWarpsPerBlock + warp;
-    const int64_t span_lo = p.num_bags / nw * gw + min(gw, p.num_bags % nw);
-    const int64_t span_hi = span_lo + p.num_bags / nw + (gw < p.num_bags % nw ? 1 : 0);
+    const int64_t span_lo = gw * p.span;
+    const int64_t span_hi = min(p.num_bags, span_lo + p.span);
     if (span_lo >= span_hi) return;
+    // One mbarrier per warp; every lane arrives once per round of staged rows.
+    if (lane == 0) mbar_init(bar, kWarp);
+    __syncwarp();
+    uint32_t parity = 0;
 
     int t;
     int64_t b;
@@ -1083,16 +1263,13 @@ tbe_pooled_kernel(const LookupParams p)
         const int64_t run_end = min(span_hi, i + (p.B - b));   // the bags left in table t, or in the span
         const TableMeta m = load_meta(p, t);
         if (m.D > 0) {
-            const bool fast = m.rows_aligned && (m.D & 15) == 0 && m.D <= 512 && m.stride < (1ll << 32) &&
-                              (m.ty == TBE_B200_INT8 || m.ty == TBE_B200_INT4);
-            if (fast) {
-                if (m.ty == TBE_B200_INT8) {
-                    if (weighted) pool_run_fast_by_width<TBE_B200_INT8, IdxT, true>(p, m, i, run_end, b, lane, wsm);
-                    else pool_run_fast_by_width<TBE_B200_INT8, IdxT, false>(p, m, i, run_end, b, lane, wsm);
-                } else {
-                    if (weighted) pool_run_fast_by_width<TBE_B200_INT4, IdxT, true>(p, m, i, run_end, b, lane, wsm);
-                    else pool_run_fast_by_width<TBE_B200_INT4, IdxT, false>(p, m, i, run_end, b, lane, wsm);
-                }
+            const bool staged = m.rows_aligned && (m.D & 15) == 0 && m.D <= 512 && m.stride < (1ll << 32) &&
+                                (m.ty == TBE_B200_INT8 || m.ty == TBE_B200_INT4 || m.ty == TBE_B200_FP8 ||
+                                 m.ty == TBE_B200_FP16 || m.ty == TBE_B200_FP32);
+            if (staged) {
+                const bool ok = weighted ? pool_run_staged_by_type<IdxT, true>(p, m, i, run_end, b, lane, wsm, bar, parity)
+                                         : pool_run_staged_by_type<IdxT, false>(p, m, i, run_end, b, lane, wsm, bar, parity);
+                if (!ok) return;   // a bounded wait ran out; the error flag says so
             } else {
                 pool_run_general<IdxT>(p, m, i, run_end, b, lane, wsm);
             }
@@ -1143,8 +1320,10 @@ tbe_nobag_kernel(const LookupParams p, int64_t num_indices, int max_D)
     for (int e = D + lane; e < max_D; e += kWarp) store_scalar(seg, e, 0.0f, p.out_ty);
 }
 
+constexpr int kSpanLarge = 16;   // bags per warp when there is plenty of work; a multiple of every group count
+
 template <typename IdxT, int MINB>
-int launch_pooled(const LookupParams& p, cudaStream_t s)
+int launch_pooled(LookupParams p, int max_D, cudaStream_t s)
 {
     static int resident = 0;   // blocks that fit on one SM (occupancy query, once)
     if (resident == 0) {
@@ -1155,12 +1334,23 @@ int launch_pooled(const LookupParams& p, cudaStream_t s)
         }
         resident = n;
     }
-    // Persistent launch: as many blocks as stay resident (a multiple of the SM count), each warp striding
-    // over the bags; fewer when there are fewer bags than warps.
-    const int64_t need = (p.num_bags + kWarpsPerBlock - 1) / kWarpsPerBlock;
-    const int64_t fit = static_cast<int64_t>(sm_count()) * resident;
-    const unsigned blocks = static_cast<unsigned>(need < fit ? need : fit);
-    tbe_pooled_kernel<IdxT, MINB><<<blocks, kWarpsPerBlock * kWarp, 0, s>>>(p);
+    // Plenty of bags: fixed spans, as many blocks as that takes; the hardware block scheduler evens out the
+    // load.  Otherwise one span per resident warp, rounded up to the number of bags a warp pools side by
+    // side for rows of max_D elements, so that a warp's last step is not a mostly idle one.
+    const int64_t slots = static_cast<int64_t>(sm_count()) * resident * kWarpsPerBlock;
+    if (p.num_bags >= slots * kSpanLarge) {
+        p.span = kSpanLarge;
+    } else {
+        int lpr = 2;
+        while (lpr < 32 && lpr * 16 < max_D) lpr <<= 1;
+        const int64_t grain = kWarp / lpr;
+        const int64_t per = (p.num_bags + slots - 1) / slots;
+        p.span = per < grain ? per : grain;
+    }
+    const int64_t warps = (p.num_bags + p.span - 1) / p.span;
+    const int64_t blocks = (warps + kWarpsPerBlock - 1) / kWarpsPerBlock;
+    if (blocks > 0x7fffffffll) return fail(TBE_B200_ERR_UNSUPPORTED, "lookup: too many bags for one launch");
+    tbe_pooled_kernel<IdxT, MINB><<<static_cast<unsigned>(blocks), kWarpsPerBlock * kWarp, 0, s>>>(p);
     return check_launch("tbe_pooled_kernel");
 }
 
@@ -1206,6 +1396,7 @@ extern "C" int tbe_b200_int_nbit_lookup(const tbe_b200_lookup_args* a, tbe_b200_
     p.num_indices = a->num_indices;
     p.out_stride = a->output_stride;
     p.rows_per_dest = a->rows_per_dest;
+    p.span = 1;
     p.T = a->T;
     p.B32 = (p.num_bags < (1ll << 32) && a->B > 0) ? static_cast<uint32_t>(a->B) : 0u;
     p.pooling_mode = a->pooling_mode;
@@ -1229,5 +1420,6 @@ extern "C" int tbe_b200_int_nbit_lookup(const tbe_b200_lookup_args* a, tbe_b200_
         return check_launch("tbe_nobag_kernel");
     }
     if (p.num_bags == 0) return TBE_B200_OK;
-    return a->index_bits == 32 ? launch_pooled<int32_t, kMinBlocksPerSM>(p, s) : launch_pooled<int64_t, kMinBlocksPerSM>(p, s);
+    return a->index_bits == 32 ? launch_pooled<int32_t, kMinBlocksPerSM>(p, a->max_D, s)
+                               : launch_pooled<int64_t, kMinBlocksPerSM>(p, a->max_D, s);
 }
