@@ -388,7 +388,16 @@ def main():
     ap.add_argument("--scale-e", type=float, default=1.0, help="scale rows per table (small cases for profiling)")
     ap.add_argument("--scale-b", type=float, default=1.0, help="scale the batch size (small cases for profiling)")
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
+    ap.add_argument("--probe-gather", action="store_true",
+                    help="run the row-gather ceiling probe (rows/s the memory system delivers for scattered rows, "
+                         "no dequantisation) instead of the benchmark")
+    ap.add_argument("--probe-max-gib", type=float, default=120.0, help="largest table the probe may allocate")
     args = ap.parse_args()
+    if args.probe_gather:
+        probe = os.path.join(ROOT, "fbgemm_ascend_b200", "lib", "tbe_b200_row_gather_probe")
+        if not os.path.exists(probe):
+            raise SystemExit(f"{probe} is missing: run `python -m fbgemm_ascend_b200.build`")
+        raise SystemExit(subprocess.call([probe, str(args.probe_max_gib)]))
     if args.impl == "reference":
         run_reference_arm(args)
         return

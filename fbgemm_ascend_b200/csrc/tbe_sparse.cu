@@ -1,0 +1,349 @@
+// Producers of the lookup's inputs on B200 (sm_100a): lengths -> offsets, and the reordering of a
+// jagged request (lengths / values / weights) by table.
+//
+//   complete cumsum     out[0] = 0, out[i + 1] = in[0] + ... + in[i]            (int32 / int64)
+//       replaces aclnnAsynchronousCompleteCumsum
+//       (reference: src/sparse_ops/asynchronous_complete_cumsum/asynchronous_complete_cumsum.cpp:14-54)
+//   permute 2D sparse   out_lengths[i, :] = lengths[permute[i], :]; out_values = the value segments of the
+//       tables permute[0], permute[1], ... one after the other; weights alike
+//       replaces aclnnPermute2dSparseData
+//       (reference: src/sparse_ops/permute2d_sparse_data/permute2d_sparse_data.cpp:45-150, permute1d_sparse_data.cpp:81-165)
+//
+// Both are streaming integer work bounded by HBM bandwidth.  Both need a little global memory beyond
+// their inputs and outputs (per-tile sums; per-table segment lengths and offsets): the caller passes it.
+#include "tbe_common.cuh"
+
+namespace tbe {
+
+namespace {
+
+constexpr int kScanThreads = 256;
+constexpr int kScanPerThread = 8;
+constexpr int kScanTile = kScanThreads * kScanPerThread;   // elements per block
+
+__device__ __forceinline__ int64_t warp_sum(int64_t v)
+{
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) v += __shfl_xor_sync(0xffffffffu, v, d);
+    return v;
+}
+
+// Sum over the block; every thread gets the result.  `red` holds one value per warp.
+__device__ __forceinline__ int64_t block_sum(int64_t v, int64_t* red)
+{
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    v = warp_sum(v);
+    __syncthreads();   // `red` may still be read from an earlier call
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    int64_t t = 0;
+    for (int w = 0; w < (blockDim.x >> 5); ++w) t += red[w];
+    return t;
+}
+
+// ---- complete cumsum: tile sums, then every tile scans itself behind the sum of the tiles before it ----
+
+template <typename T>
+__global__ void __launch_bounds__(kScanThreads) tile_sums_kernel(const T* __restrict__ in, int64_t n, int64_t* __restrict__ tile_sums)
+{
+    __shared__ int64_t red[kScanThreads / 32];
+    const int64_t base = static_cast<int64_t>(blockIdx.x) * kScanTile;
+    int64_t s = 0;
+#pragma unroll
+    for (int j = 0; j < kScanPerThread; ++j) {
+        const int64_t i = base + j * kScanThreads + threadIdx.x;
+        if (i < n) s += static_cast<int64_t>(in[i]);
+    }
+    s = block_sum(s, red);
+    if (threadIdx.x == 0) tile_sums[blockIdx.x] = s;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kScanThreads) scan_tiles_kernel(const T* __restrict__ in, int64_t n, const int64_t* __restrict__ tile_sums,
+                                                                   T* __restrict__ out)
+{
+    __shared__ int64_t red[kScanThreads / 32];
+    __shared__ int64_t warp_base[kScanThreads / 32];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    // everything before this tile
+    int64_t before = 0;
+    for (int64_t t = threadIdx.x; t < blockIdx.x; t += kScanThreads) before += tile_sums[t];
+    before = block_sum(before, red);
+    // thread-contiguous elements: thread i owns [base + 8i, base + 8i + 8)
+    const int64_t first = static_cast<int64_t>(blockIdx.x) * kScanTile + static_cast<int64_t>(threadIdx.x) * kScanPerThread;
+    int64_t v[kScanPerThread];
+    int64_t mine = 0;
+#pragma unroll
+    for (int j = 0; j < kScanPerThread; ++j) {
+        v[j] = (first + j < n) ? static_cast<int64_t>(in[first + j]) : 0;
+        mine += v[j];
+    }
+    // exclusive scan of the per-thread sums: within the warp by shuffles, across warps through shared memory
+    int64_t incl = mine;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+        const int64_t up = __shfl_up_sync(0xffffffffu, incl, d);
+        if (lane >= d) incl += up;
+    }
+    if (lane == 31) warp_base[warp] = incl;
+    __syncthreads();
+    int64_t run = before + (incl - mine);
+    for (int w = 0; w < warp; ++w) run += warp_base[w];
+    if (blockIdx.x == 0 && threadIdx.x == 0) out[0] = 0;
+#pragma unroll
+    for (int j = 0; j < kScanPerThread; ++j) {
+        run += v[j];
+        if (first + j < n) out[first + j + 1] = static_cast<T>(run);
+    }
+}
+
+// ---- permute 2D sparse data ----------------------------------------------------------------------------
+
+// seg_len[t] += sum of a slice of lengths[t, :]  (seg_len cleared beforehand)
+template <typename T>
+__global__ void __launch_bounds__(256) segment_lengths_kernel(const T* __restrict__ lengths, int64_t B, int64_t* __restrict__ seg_len)
+{
+    __shared__ int64_t red[8];
+    const int64_t t = blockIdx.y;
+    const T* row = lengths + t * B;
+    int64_t s = 0;
+    for (int64_t b = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; b < B; b += static_cast<int64_t>(gridDim.x) * blockDim.x)
+        s += static_cast<int64_t>(row[b]);
+    s = block_sum(s, red);
+    if (threadIdx.x == 0 && s != 0) atomicAdd(reinterpret_cast<unsigned long long*>(seg_len + t), static_cast<unsigned long long>(s));
+}
+
+// One block: in_off = exclusive sums of seg_len over the input tables; out_off = exclusive sums of
+// seg_len[permute[i]] over the output tables.  An entry of `permute` outside [0, T_in) counts as an empty table
+// and sets the error flag.
+__global__ void __launch_bounds__(kScanThreads) segment_offsets_kernel(const int64_t* __restrict__ seg_len, int64_t T_in,
+                                                                        const int32_t* __restrict__ permute, int64_t T_out,
+                                                                        int64_t* __restrict__ in_off, int64_t* __restrict__ out_off,
+                                                                        int32_t* error_flag)
+{
+    __shared__ int64_t warp_base[kScanThreads / 32];
+    __shared__ int64_t carry;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    for (int pass = 0; pass < 2; ++pass) {
+        const int64_t count = pass == 0 ? T_in : T_out;
+        int64_t* off = pass == 0 ? in_off : out_off;
+        if (threadIdx.x == 0) {
+            carry = 0;
+            off[0] = 0;
+        }
+        __syncthreads();
+        for (int64_t base = 0; base < count; base += kScanThreads) {
+            const int64_t i = base + threadIdx.x;
+            int64_t v = 0;
+            if (i < count) {
+                if (pass == 0) {
+                    v = seg_len[i];
+                } else {
+                    const int64_t p = permute[i];
+                    if (p >= 0 && p < T_in) v = seg_len[p];
+                    else if (error_flag) atomicOr(error_flag, 1);
+                }
+            }
+            int64_t incl = v;
+#pragma unroll
+            for (int d = 1; d < 32; d <<= 1) {
+                const int64_t up = __shfl_up_sync(0xffffffffu, incl, d);
+                if (lane >= d) incl += up;
+            }
+            if (lane == 31) warp_base[warp] = incl;
+            __syncthreads();
+            int64_t run = carry + incl;
+            for (int w = 0; w < warp; ++w) run += warp_base[w];
+            if (i < count) off[i + 1] = run;
+            __syncthreads();
+            if (threadIdx.x == kScanThreads - 1) carry = run;
+            __syncthreads();
+        }
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) permute_lengths_kernel(const T* __restrict__ lengths, int64_t T_in, int64_t B,
+                                                              const int32_t* __restrict__ permute, T* __restrict__ out)
+{
+    const int64_t i = blockIdx.y;
+    const int64_t p = permute[i];
+    const bool ok = p >= 0 && p < T_in;
+    for (int64_t b = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; b < B; b += static_cast<int64_t>(gridDim.x) * blockDim.x)
+        out[i * B + b] = ok ? lengths[p * B + b] : static_cast<T>(0);
+}
+
+// Output position o lies in output table i with out_off[i] <= o < out_off[i + 1]; its source is
+// in_off[permute[i]] + (o - out_off[i]).  A thread finds the table of its first position by binary search
+// and walks forward from there.  VT is the unit copied per position (the element, or 16 bytes of a wide row).
+template <typename VT>
+__global__ void __launch_bounds__(256) permute_segments_kernel(const VT* __restrict__ src, VT* __restrict__ dst, int64_t units_per_pos,
+                                                               int64_t capacity /* positions */, const int32_t* __restrict__ permute,
+                                                               int64_t T_in, int64_t T_out, const int64_t* __restrict__ in_off,
+                                                               const int64_t* __restrict__ out_off)
+{
+    const int64_t total = min(capacity, out_off[T_out]) * units_per_pos;
+    const int64_t step = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    int64_t i = -1;        // current output table
+    int64_t seg_lo = 0, seg_hi = 0, delta = 0;
+    for (int64_t u = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; u < total; u += step) {
+        const int64_t o = u / units_per_pos;
+        if (i < 0 || o >= seg_hi) {
+            // largest i with out_off[i] <= o
+            int64_t lo = (i < 0) ? 0 : i, hi = T_out;
+            while (hi - lo > 1) {
+                const int64_t mid = (lo + hi) >> 1;
+                if (out_off[mid] <= o) lo = mid; else hi = mid;
+            }
+            i = lo;
+            seg_lo = out_off[i];
+            seg_hi = out_off[i + 1];
+            const int64_t p = permute[i];
+            delta = ((p >= 0 && p < T_in) ? in_off[p] : 0) - seg_lo;
+        }
+        dst[u] = src[u + delta * units_per_pos];
+    }
+}
+
+template <typename VT>
+int launch_segments(const void* src, void* dst, int64_t units_per_pos, int64_t capacity, const int32_t* permute, int64_t T_in,
+                    int64_t T_out, const int64_t* in_off, const int64_t* out_off, cudaStream_t s)
+{
+    const int64_t units = capacity * units_per_pos;
+    if (units <= 0) return TBE_B200_OK;
+    const int64_t want = (units + 256 * 4 - 1) / (256 * 4);   // about four units per thread
+    const int64_t cap = static_cast<int64_t>(sm_count()) * 32;
+    const unsigned blocks = static_cast<unsigned>(want < cap ? want : cap);
+    permute_segments_kernel<VT><<<blocks, 256, 0, s>>>(static_cast<const VT*>(src), static_cast<VT*>(dst), units_per_pos, capacity, permute,
+                                                       T_in, T_out, in_off, out_off);
+    return check_launch("permute_segments_kernel");
+}
+
+int copy_segments(const void* src, void* dst, int64_t row_bytes, int64_t capacity, const int32_t* permute, int64_t T_in, int64_t T_out,
+                  const int64_t* in_off, const int64_t* out_off, cudaStream_t s)
+{
+    const uintptr_t both = reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst);
+    if (row_bytes % 16 == 0 && both % 16 == 0)
+        return launch_segments<uint4>(src, dst, row_bytes / 16, capacity, permute, T_in, T_out, in_off, out_off, s);
+    if (row_bytes % 8 == 0 && both % 8 == 0)
+        return launch_segments<uint64_t>(src, dst, row_bytes / 8, capacity, permute, T_in, T_out, in_off, out_off, s);
+    if (row_bytes % 4 == 0 && both % 4 == 0)
+        return launch_segments<uint32_t>(src, dst, row_bytes / 4, capacity, permute, T_in, T_out, in_off, out_off, s);
+    if (row_bytes % 2 == 0 && both % 2 == 0)
+        return launch_segments<uint16_t>(src, dst, row_bytes / 2, capacity, permute, T_in, T_out, in_off, out_off, s);
+    return launch_segments<uint8_t>(src, dst, row_bytes, capacity, permute, T_in, T_out, in_off, out_off, s);
+}
+
+}  // namespace
+
+// Shared by the entry point that takes the caller's scratch and by any that brings its own.
+int complete_cumsum_launch(const void* in, int64_t n, int index_bits, void* out, int64_t* tile_sums, cudaStream_t s)
+{
+    const int64_t tiles = (n + kScanTile - 1) / kScanTile;
+    if (index_bits == 32) {
+        if (tiles > 1) tile_sums_kernel<int32_t><<<static_cast<unsigned>(tiles), kScanThreads, 0, s>>>(static_cast<const int32_t*>(in), n, tile_sums);
+        scan_tiles_kernel<int32_t><<<static_cast<unsigned>(tiles), kScanThreads, 0, s>>>(static_cast<const int32_t*>(in), n, tile_sums,
+                                                                                        static_cast<int32_t*>(out));
+    } else {
+        if (tiles > 1) tile_sums_kernel<int64_t><<<static_cast<unsigned>(tiles), kScanThreads, 0, s>>>(static_cast<const int64_t*>(in), n, tile_sums);
+        scan_tiles_kernel<int64_t><<<static_cast<unsigned>(tiles), kScanThreads, 0, s>>>(static_cast<const int64_t*>(in), n, tile_sums,
+                                                                                        static_cast<int64_t*>(out));
+    }
+    return check_launch("complete_cumsum");
+}
+
+int64_t complete_cumsum_tiles(int64_t n) { return (n + kScanTile - 1) / kScanTile; }
+
+}  // namespace tbe
+
+extern "C" int64_t tbe_b200_complete_cumsum_scratch_bytes(int64_t n)
+{
+    const int64_t tiles = tbe::complete_cumsum_tiles(n < 0 ? 0 : n);
+    return tiles > 1 ? tiles * 8 : 0;
+}
+
+extern "C" int tbe_b200_complete_cumsum(const void* in, int64_t n, int index_bits, void* out, void* scratch, int64_t scratch_bytes,
+                                        tbe_b200_stream_t stream)
+{
+    using namespace tbe;
+    if (n < 0) return fail(TBE_B200_ERR_INVALID_ARGUMENT, "complete_cumsum: n must be non-negative");
+    if (index_bits != 32 && index_bits != 64)
+        return fail(TBE_B200_ERR_INVALID_ARGUMENT, "complete_cumsum: index_bits must be 32 or 64, got %d", index_bits);
+    if (!out || (n > 0 && !in)) return fail(TBE_B200_ERR_INVALID_ARGUMENT, "complete_cumsum: a required pointer is NULL");
+    cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+    if (n == 0) {
+        if (cudaMemsetAsync(out, 0, index_bits / 8, s) != cudaSuccess) return fail(TBE_B200_ERR_CUDA, "complete_cumsum: memset failed");
+        return TBE_B200_OK;
+    }
+    const int64_t need = tbe_b200_complete_cumsum_scratch_bytes(n);
+    if (need > 0 && (!scratch || scratch_bytes < need))
+        return fail(TBE_B200_ERR_INVALID_ARGUMENT, "complete_cumsum: %lld bytes of scratch are needed, got %lld", static_cast<long long>(need),
+                    static_cast<long long>(scratch ? scratch_bytes : 0));
+    if (complete_cumsum_tiles(n) > 0x7fffffffll) return fail(TBE_B200_ERR_UNSUPPORTED, "complete_cumsum: too many elements for one launch");
+    return complete_cumsum_launch(in, n, index_bits, out, static_cast<int64_t*>(scratch), s);
+}
+
+extern "C" int64_t tbe_b200_permute_2d_sparse_scratch_bytes(int64_t T_in, int64_t T_out)
+{
+    if (T_in < 0 || T_out < 0) return 0;
+    return (T_in + (T_in + 1) + (T_out + 1)) * 8;
+}
+
+// Scratch layout: seg_len[T_in], in_off[T_in + 1], out_off[T_out + 1], all int64.
+extern "C" int tbe_b200_permute_2d_sparse_offsets(const int32_t* permute, int64_t T_out, const void* lengths, int lengths_bits, int64_t T_in,
+                                                  int64_t B, void* out_lengths, void* scratch, int64_t scratch_bytes, int32_t* error_flag,
+                                                  tbe_b200_stream_t stream)
+{
+    using namespace tbe;
+    if (T_in <= 0 || T_out <= 0 || B <= 0) return fail(TBE_B200_ERR_INVALID_ARGUMENT, "permute_2d_sparse: T_in, T_out and B must be positive");
+    if (lengths_bits != 32 && lengths_bits != 64)
+        return fail(TBE_B200_ERR_INVALID_ARGUMENT, "permute_2d_sparse: lengths must be int32 or int64, got %d bits", lengths_bits);
+    if (!permute || !lengths || !out_lengths || !scratch) return fail(TBE_B200_ERR_INVALID_ARGUMENT, "permute_2d_sparse: a required pointer is NULL");
+    if (scratch_bytes < tbe_b200_permute_2d_sparse_scratch_bytes(T_in, T_out))
+        return fail(TBE_B200_ERR_INVALID_ARGUMENT, "permute_2d_sparse: %lld bytes of scratch are needed, got %lld",
+                    static_cast<long long>(tbe_b200_permute_2d_sparse_scratch_bytes(T_in, T_out)), static_cast<long long>(scratch_bytes));
+    if (T_in > 65535 || T_out > 65535) return fail(TBE_B200_ERR_UNSUPPORTED, "permute_2d_sparse: at most 65535 tables");
+    cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+    int64_t* seg_len = static_cast<int64_t*>(scratch);
+    int64_t* in_off = seg_len + T_in;
+    int64_t* out_off = in_off + T_in + 1;
+    if (cudaMemsetAsync(seg_len, 0, static_cast<size_t>(T_in) * 8, s) != cudaSuccess)
+        return fail(TBE_B200_ERR_CUDA, "permute_2d_sparse: memset failed");
+    const int64_t per_row = (B + 256 * 8 - 1) / (256 * 8);
+    const unsigned gx = static_cast<unsigned>(per_row < 64 ? per_row : 64);
+    if (lengths_bits == 32) {
+        segment_lengths_kernel<int32_t><<<dim3(gx, static_cast<unsigned>(T_in)), 256, 0, s>>>(static_cast<const int32_t*>(lengths), B, seg_len);
+    } else {
+        segment_lengths_kernel<int64_t><<<dim3(gx, static_cast<unsigned>(T_in)), 256, 0, s>>>(static_cast<const int64_t*>(lengths), B, seg_len);
+    }
+    segment_offsets_kernel<<<1, kScanThreads, 0, s>>>(seg_len, T_in, permute, T_out, in_off, out_off, error_flag);
+    if (lengths_bits == 32) {
+        permute_lengths_kernel<int32_t><<<dim3(gx, static_cast<unsigned>(T_out)), 256, 0, s>>>(static_cast<const int32_t*>(lengths), T_in, B, permute,
+                                                                                                static_cast<int32_t*>(out_lengths));
+    } else {
+        permute_lengths_kernel<int64_t><<<dim3(gx, static_cast<unsigned>(T_out)), 256, 0, s>>>(static_cast<const int64_t*>(lengths), T_in, B, permute,
+                                                                                                static_cast<int64_t*>(out_lengths));
+    }
+    return check_launch("permute_2d_sparse_offsets");
+}
+
+extern "C" int tbe_b200_permute_2d_sparse_copy(const int32_t* permute, int64_t T_out, int64_t T_in, const void* values, int64_t value_bytes,
+                                               const void* weights, int64_t weight_row_bytes, void* out_values, void* out_weights,
+                                               int64_t out_capacity, const void* scratch, tbe_b200_stream_t stream)
+{
+    using namespace tbe;
+    if (T_in <= 0 || T_out <= 0) return fail(TBE_B200_ERR_INVALID_ARGUMENT, "permute_2d_sparse: T_in and T_out must be positive");
+    if (out_capacity < 0) return fail(TBE_B200_ERR_INVALID_ARGUMENT, "permute_2d_sparse: out_capacity must be non-negative");
+    if (!permute || !scratch) return fail(TBE_B200_ERR_INVALID_ARGUMENT, "permute_2d_sparse: a required pointer is NULL");
+    if (out_capacity == 0) return TBE_B200_OK;
+    if (!values || !out_values || value_bytes <= 0) return fail(TBE_B200_ERR_INVALID_ARGUMENT, "permute_2d_sparse: values are missing");
+    if (weights && (!out_weights || weight_row_bytes <= 0)) return fail(TBE_B200_ERR_INVALID_ARGUMENT, "permute_2d_sparse: weights output is missing");
+    cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+    const int64_t* seg_len = static_cast<const int64_t*>(scratch);
+    const int64_t* in_off = seg_len + T_in;
+    const int64_t* out_off = in_off + T_in + 1;
+    int rc = copy_segments(values, out_values, value_bytes, out_capacity, permute, T_in, T_out, in_off, out_off, s);
+    if (rc != TBE_B200_OK) return rc;
+    if (weights) rc = copy_segments(weights, out_weights, weight_row_bytes, out_capacity, permute, T_in, T_out, in_off, out_off, s);
+    return rc;
+}

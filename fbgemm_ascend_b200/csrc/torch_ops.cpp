@@ -22,6 +22,7 @@
 
 #include <algorithm>
 #include <optional>
+#include <tuple>
 #include <vector>
 
 #include "tbe_b200.h"
@@ -326,6 +327,128 @@ Tensor permute_pooled_embs_auto_grad(const Tensor& pooled_embs, const Tensor& of
     return PermutePooledEmbsFunction::apply(pooled_embs, offset_dim_list, permute_list, inv_offset_dim_list, inv_permute_list);
 }
 
+// ---- lengths -> offsets (asynchronous_complete_cumsum.cpp:14-57) -------------------------------
+
+Tensor asynchronous_complete_cumsum_cuda(const Tensor& offset)
+{
+    check_cuda(offset, "offset");
+    TORCH_CHECK(offset.dim() == 1, "offset must be 1D");
+    TORCH_CHECK(offset.scalar_type() == at::kInt || offset.scalar_type() == at::kLong, "offset must be int32 or int64");
+    const c10::cuda::CUDAGuard guard(offset.device());
+    const Tensor in = offset.contiguous();
+    const int64_t n = in.size(0);
+    Tensor out = at::empty({n + 1}, in.options());
+    const int64_t need = tbe_b200_complete_cumsum_scratch_bytes(n);
+    Tensor scratch = at::empty({need}, in.options().dtype(at::kByte));   // caching-allocator blocks are 512-byte aligned
+    check_status(tbe_b200_complete_cumsum(n ? in.data_ptr() : nullptr, n, in.scalar_type() == at::kInt ? 32 : 64, out.data_ptr(),
+                                          need ? scratch.data_ptr() : nullptr, need, current_stream()),
+                 "asynchronous_complete_cumsum");
+    return out;
+}
+
+Tensor asynchronous_inclusive_cumsum_cuda(const Tensor& offset)
+{
+    if (offset.numel() == 0) return at::empty_like(offset);
+    const Tensor all = asynchronous_complete_cumsum_cuda(offset);
+    return all.narrow(0, 1, all.size(0) - 1);
+}
+
+Tensor asynchronous_exclusive_cumsum_cuda(const Tensor& offset)
+{
+    if (offset.numel() == 0) return at::empty_like(offset);
+    const Tensor all = asynchronous_complete_cumsum_cuda(offset);
+    return all.narrow(0, 0, all.size(0) - 1);
+}
+
+// ---- jagged request reordered by table (permute2d_sparse_data.cpp:45-150, permute1d_sparse_data.cpp:81-165) ----
+
+using SparseTuple = std::tuple<Tensor, Tensor, std::optional<Tensor>>;
+
+// lengths2d is [T_in, B]; the caller reshapes the returned lengths.
+SparseTuple permute_sparse_common(const Tensor& permute, const Tensor& lengths2d, const Tensor& values,
+                                  const std::optional<Tensor>& weights, const std::optional<int64_t>& permuted_lengths_sum,
+                                  const char* op)
+{
+    check_cuda(permute, "permute");
+    check_cuda(lengths2d, "lengths");
+    check_cuda(values, "values");
+    TORCH_CHECK(permute.dim() == 1, "permute must be 1D");
+    TORCH_CHECK(permute.scalar_type() == at::kInt, "permute must be int32");
+    TORCH_CHECK(lengths2d.scalar_type() == at::kInt || lengths2d.scalar_type() == at::kLong, "lengths must be int32 or int64");
+    if (weights.has_value()) {
+        check_cuda(*weights, "weights");
+        TORCH_CHECK(weights->dim() == 1 || weights->dim() == 2, "weights must be 1D [L] or 2D [L, D]");
+        TORCH_CHECK(weights->size(0) == values.size(0), "weights and values length mismatch: ", weights->size(0), " vs ", values.size(0));
+    }
+    if (permuted_lengths_sum.has_value())
+        TORCH_CHECK(*permuted_lengths_sum >= 0, "permuted_lengths_sum must be non-negative, got ", *permuted_lengths_sum);
+    const c10::cuda::CUDAGuard guard(values.device());
+    const Tensor perm = permute.contiguous();
+    const Tensor len = lengths2d.contiguous();
+    const Tensor val = values.contiguous();
+    const int64_t T_out = perm.size(0), T_in = len.size(0), B = len.size(1);
+    if (T_in == 0 || B == 0 || T_out == 0)
+        return SparseTuple(len.clone(), val.clone(), weights.has_value() ? std::make_optional(weights->contiguous().clone()) : std::nullopt);
+    Tensor out_len = at::empty({T_out, B}, len.options());
+    const int64_t sbytes = tbe_b200_permute_2d_sparse_scratch_bytes(T_in, T_out);
+    Tensor scratch = at::empty({sbytes / 8}, len.options().dtype(at::kLong));
+    check_status(tbe_b200_permute_2d_sparse_offsets(perm.data_ptr<int32_t>(), T_out, len.data_ptr(), len.scalar_type() == at::kInt ? 32 : 64,
+                                                    T_in, B, out_len.data_ptr(), scratch.data_ptr(), sbytes, nullptr, current_stream()),
+                 op);
+    // Without permuted_lengths_sum the output size has to be read back, as in the reference (.item(), :106-112).
+    const int64_t total = permuted_lengths_sum.has_value() ? *permuted_lengths_sum : scratch[sbytes / 8 - 1].item<int64_t>();
+    Tensor out_val = at::empty({total}, val.options());
+    std::optional<Tensor> out_w;
+    Tensor w;
+    int64_t w_row_bytes = 0;
+    if (weights.has_value()) {
+        w = weights->contiguous();
+        const int64_t cols = w.dim() == 2 ? w.size(1) : 1;
+        w_row_bytes = cols * w.element_size();
+        out_w = w.dim() == 2 ? at::empty({total, cols}, w.options()) : at::empty({total}, w.options());
+    }
+    if (total > 0)
+        check_status(tbe_b200_permute_2d_sparse_copy(perm.data_ptr<int32_t>(), T_out, T_in, val.data_ptr(), val.element_size(),
+                                                     weights.has_value() ? w.data_ptr() : nullptr, w_row_bytes, out_val.data_ptr(),
+                                                     out_w.has_value() ? out_w->data_ptr() : nullptr, total, scratch.data_ptr(),
+                                                     current_stream()),
+                     op);
+    return SparseTuple(out_len, out_val, out_w);
+}
+
+SparseTuple permute_2d_sparse_data_cuda(const Tensor& permute, const Tensor& lengths, const Tensor& values,
+                                        const std::optional<Tensor>& weights, std::optional<c10::SymInt> permuted_lengths_sum)
+{
+    TORCH_CHECK(lengths.dim() == 2, "lengths must be 2D");
+    std::optional<int64_t> sum;
+    if (permuted_lengths_sum.has_value()) sum = permuted_lengths_sum->guard_int(__FILE__, __LINE__);
+    return permute_sparse_common(permute, lengths, values, weights, sum, "permute_2D_sparse_data");
+}
+
+SparseTuple permute_2d_sparse_data_input1d_cuda(const Tensor& permute, const Tensor& lengths, const Tensor& values, int64_t stride,
+                                                const std::optional<Tensor>& weights, std::optional<c10::SymInt> permuted_lengths_sum)
+{
+    TORCH_CHECK(lengths.dim() == 1, "lengths must be 1D");
+    TORCH_CHECK(stride > 0 && lengths.numel() % stride == 0, "lengths of ", lengths.numel(), " elements do not split into rows of ", stride);
+    std::optional<int64_t> sum;
+    if (permuted_lengths_sum.has_value()) sum = permuted_lengths_sum->guard_int(__FILE__, __LINE__);
+    auto r = permute_sparse_common(permute, lengths.view({-1, stride}), values, weights, sum, "permute_2D_sparse_data_input1D");
+    return SparseTuple(std::get<0>(r).view({-1}), std::get<1>(r), std::get<2>(r));
+}
+
+SparseTuple permute_1d_sparse_data_cuda(const Tensor& permute, const Tensor& lengths, const Tensor& values,
+                                        const std::optional<Tensor>& weights, std::optional<c10::SymInt> permuted_lengths_sum)
+{
+    TORCH_CHECK(permute.dim() == 1, "permute must be 1D");
+    TORCH_CHECK(lengths.dim() == 1, "lengths must be 1D");
+    TORCH_CHECK(values.dim() == 1, "values must be 1D");
+    if (weights.has_value()) TORCH_CHECK(weights->numel() > 0 || values.numel() == 0, "weights must not be empty");
+    std::optional<int64_t> sum;
+    if (permuted_lengths_sum.has_value()) sum = permuted_lengths_sum->guard_int(__FILE__, __LINE__);
+    auto r = permute_sparse_common(permute, lengths.view({-1, 1}), values, weights, sum, "permute_1D_sparse_data");
+    return SparseTuple(std::get<0>(r).view({-1}), std::get<1>(r), std::get<2>(r));
+}
+
 bool has_schema(const char* qualified_name)
 {
     return c10::Dispatcher::singleton().findSchema({qualified_name, ""}).has_value();
@@ -335,6 +458,36 @@ void def_if_absent(torch::Library& m, const char* ns, const char* name, const ch
 {
     const std::string q = std::string(ns) + "::" + name;
     if (!has_schema(q.c_str())) m.def(schema);
+}
+
+void def_sparse_schemas(torch::Library& m, const char* ns)
+{
+    def_if_absent(m, ns, "asynchronous_complete_cumsum", "asynchronous_complete_cumsum(Tensor offset) -> Tensor");
+    def_if_absent(m, ns, "asynchronous_inclusive_cumsum", "asynchronous_inclusive_cumsum(Tensor offset) -> Tensor");
+    def_if_absent(m, ns, "asynchronous_exclusive_cumsum", "asynchronous_exclusive_cumsum(Tensor offset) -> Tensor");
+    def_if_absent(m, ns, "permute_2D_sparse_data",
+                  "permute_2D_sparse_data(Tensor permute, Tensor lengths, Tensor values, Tensor? weights=None, "
+                  "SymInt? permuted_lengths_sum=None) -> (Tensor, Tensor, Tensor?)");
+    def_if_absent(m, ns, "permute_sparse_data",
+                  "permute_sparse_data(Tensor permute, Tensor lengths, Tensor values, Tensor? weights=None, "
+                  "SymInt? permuted_lengths_sum=None) -> (Tensor, Tensor, Tensor?)");
+    def_if_absent(m, ns, "permute_2D_sparse_data_input1D",
+                  "permute_2D_sparse_data_input1D(Tensor permute, Tensor lengths, Tensor values, int stride, Tensor? weights=None, "
+                  "SymInt? permuted_lengths_sum=None) -> (Tensor, Tensor, Tensor?)");
+    def_if_absent(m, ns, "permute_1D_sparse_data",
+                  "permute_1D_sparse_data(Tensor permute, Tensor lengths, Tensor values, Tensor? weights=None, "
+                  "SymInt? permuted_lengths_sum=None) -> (Tensor, Tensor, Tensor?)");
+}
+
+void impl_sparse(torch::Library& m)
+{
+    m.impl("asynchronous_complete_cumsum", TORCH_FN(asynchronous_complete_cumsum_cuda));
+    m.impl("asynchronous_inclusive_cumsum", TORCH_FN(asynchronous_inclusive_cumsum_cuda));
+    m.impl("asynchronous_exclusive_cumsum", TORCH_FN(asynchronous_exclusive_cumsum_cuda));
+    m.impl("permute_2D_sparse_data", TORCH_FN(permute_2d_sparse_data_cuda));
+    m.impl("permute_sparse_data", TORCH_FN(permute_2d_sparse_data_cuda));
+    m.impl("permute_2D_sparse_data_input1D", TORCH_FN(permute_2d_sparse_data_input1d_cuda));
+    m.impl("permute_1D_sparse_data", TORCH_FN(permute_1d_sparse_data_cuda));
 }
 
 }  // namespace
@@ -362,10 +515,12 @@ TORCH_LIBRARY_FRAGMENT(fbgemm, m)
     def_if_absent(m, "fbgemm", "permute_pooled_embs_auto_grad",
                   "permute_pooled_embs_auto_grad(Tensor pooled_embs, Tensor offset_dim_list, Tensor permute_list, "
                   "Tensor inv_offset_dim_list, Tensor inv_permute_list) -> Tensor");
+    def_sparse_schemas(m, "fbgemm");
 }
 
 TORCH_LIBRARY_IMPL(fbgemm, CUDA, m)
 {
+    impl_sparse(m);
     m.impl("int_nbit_split_embedding_codegen_lookup_function", TORCH_FN(int_nbit_split_embedding_codegen_lookup_function_cuda));
     m.impl("FloatToFused8BitRowwiseQuantized", TORCH_FN(float_to_fused8bit));
     m.impl("HalfToFused8BitRowwiseQuantized", TORCH_FN(half_to_fused8bit));
@@ -381,16 +536,21 @@ TORCH_LIBRARY_IMPL(fbgemm, Autograd, m)
     m.impl("permute_pooled_embs_auto_grad", TORCH_FN(permute_pooled_embs_auto_grad));
 }
 
-// The reference also exposes the permute under its own namespace
-// (permute_pooled_embs.cpp:107-117).
+// The reference also exposes these operators under its own namespace
+// (permute_pooled_embs.cpp:107-117, asynchronous_complete_cumsum.cpp:55-67, permute2d_sparse_data.cpp:152-175).
 TORCH_LIBRARY_FRAGMENT(mxrec, m)
 {
+    def_sparse_schemas(m, "mxrec");
     def_if_absent(m, "mxrec", "permute_pooled_embs",
                   "permute_pooled_embs(Tensor pooled_embs, Tensor offset_dim_list, Tensor permute_list, "
                   "Tensor inv_offset_dim_list, Tensor inv_permute_list) -> Tensor");
 }
 
-TORCH_LIBRARY_IMPL(mxrec, CUDA, m) { m.impl("permute_pooled_embs", TORCH_FN(permute_pooled_embs_cuda)); }
+TORCH_LIBRARY_IMPL(mxrec, CUDA, m)
+{
+    m.impl("permute_pooled_embs", TORCH_FN(permute_pooled_embs_cuda));
+    impl_sparse(m);
+}
 
 // Helpers with no upstream counterpart.
 TORCH_LIBRARY_FRAGMENT(tbe_b200, m)

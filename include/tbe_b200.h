@@ -174,6 +174,42 @@ int tbe_b200_permute_pooled_embs_blocked(const void* pooled_embs, int64_t B, int
                                          const int64_t* permute_list, const int64_t* inv_offset_dim_list, int32_t T,
                                          void* output, int32_t* error_flag, tbe_b200_stream_t stream);
 
+/* ---- producers of the lookup's inputs -------------------------------------------------------- */
+
+/* Complete cumulative sum: out[0] = 0, out[i + 1] = in[0] + ... + in[i]; `in` has n elements of
+ * index_bits (32 or 64) bits, `out` n + 1 of the same type (sums wrap like the integer type does).
+ * Replaces aclnnAsynchronousCompleteCumsum, reached from asynchronous_complete_cumsum_npu
+ * (src/sparse_ops/asynchronous_complete_cumsum/asynchronous_complete_cumsum.cpp:14-37); the inclusive and
+ * exclusive forms (:39-57) are views of this result.  Inputs longer than one tile need scratch:
+ * tbe_b200_complete_cumsum_scratch_bytes(n) bytes of device memory (0 for short inputs, then scratch may be
+ * NULL), 8-byte aligned, overwritten by the call. */
+int64_t tbe_b200_complete_cumsum_scratch_bytes(int64_t n);
+int tbe_b200_complete_cumsum(const void* in, int64_t n, int index_bits, void* out, void* scratch, int64_t scratch_bytes,
+                             tbe_b200_stream_t stream);
+
+/* Reordering of a jagged request by table; replaces aclnnPermute2dSparseData, reached from
+ * permute2d_sparse_data_impl_npu (src/sparse_ops/permute2d_sparse_data/permute2d_sparse_data.cpp:45-150) and, with
+ * B = 1, permute1d_sparse_data_impl_npu (permute1d_sparse_data.cpp:81-165).  `lengths` is [T_in, B] (int32 or
+ * int64); table t owns the next sum(lengths[t, :]) entries of `values` (and rows of `weights`).  Output table i
+ * is input table permute[i] (int32; entries may repeat, T_out need not equal T_in):
+ *     out_lengths[i, :] = lengths[permute[i], :]
+ *     out_values  = values of table permute[0], then of permute[1], ...     (weights alike)
+ * Two calls, so that a caller that does not know the output size can read it in between:
+ *   _offsets  fills out_lengths and the scratch: seg_len[T_in], in_off[T_in + 1], out_off[T_out + 1], all
+ *             int64; out_off[T_out] (the last word) is the number of output values.
+ *   _copy     moves min(out_capacity, out_off[T_out]) values of value_bytes each, and as many weight rows of
+ *             weight_row_bytes (weights may be NULL), using the scratch the first call left.
+ * scratch: tbe_b200_permute_2d_sparse_scratch_bytes(T_in, T_out) bytes of device memory, 8-byte aligned.
+ * A permute entry outside [0, T_in) stands for an empty table and sets *error_flag (if given). */
+int64_t tbe_b200_permute_2d_sparse_scratch_bytes(int64_t T_in, int64_t T_out);
+int tbe_b200_permute_2d_sparse_offsets(const int32_t* permute, int64_t T_out, const void* lengths, int lengths_bits,
+                                       int64_t T_in, int64_t B, void* out_lengths, void* scratch, int64_t scratch_bytes,
+                                       int32_t* error_flag, tbe_b200_stream_t stream);
+int tbe_b200_permute_2d_sparse_copy(const int32_t* permute, int64_t T_out, int64_t T_in, const void* values,
+                                    int64_t value_bytes, const void* weights, int64_t weight_row_bytes, void* out_values,
+                                    void* out_weights, int64_t out_capacity, const void* scratch,
+                                    tbe_b200_stream_t stream);
+
 /* Message of the last failure on the calling thread ("" if none).  Host pointer,
  * valid until the next failing call on the same thread. */
 const char* tbe_b200_last_error(void);

@@ -261,3 +261,41 @@ def permute_pooled_embs(pooled: np.ndarray, offset_dim_list: np.ndarray, permute
 
 def bf16_bits_to_f32(bits: np.ndarray) -> np.ndarray:
     return (bits.astype(np.uint32) << 16).view(np.float32)
+
+
+def complete_cumsum(x: np.ndarray) -> np.ndarray:
+    """out[0] = 0, out[i + 1] = x[0] + ... + x[i], in x's integer type (sums wrap like the type does).
+
+    Restates what the reference's tests expect of ``asynchronous_complete_cumsum``
+    (bench/sparse/asynchronous_complete_cumsum_test/test_asynchronous_complete_cumsum.py:39-48: the
+    operator against the CPU operator of the same name, i.e. a zero followed by the running sums).
+    """
+    x = np.ascontiguousarray(x)
+    out = np.zeros(x.size + 1, dtype=x.dtype)
+    np.cumsum(x, out=out[1:], dtype=x.dtype)
+    return out
+
+
+def permute_2d_sparse_data(permute: np.ndarray, lengths: np.ndarray, values: np.ndarray,
+                           weights: Optional[np.ndarray] = None):
+    """(lengths[permute], value segments of the tables permute[0], permute[1], ..., weights alike).
+
+    Restates ``permute_2d_sparse_data_reference``, the CPU model the reference's own test checks the
+    operator against (bench/sparse/permute_sparse_data/test_permute2d_sparse_data.py:41-72): table t
+    owns ``sum(lengths[t, :])`` consecutive entries of ``values``; entries of ``permute`` may repeat and
+    ``len(permute)`` need not equal ``lengths.shape[0]``; 1-D or 2-D weights are cut along dim 0.
+    With an empty dimension the inputs come back unchanged (same test, :48-53).
+    """
+    lengths = np.ascontiguousarray(lengths)
+    values = np.ascontiguousarray(values)
+    if lengths.shape[0] == 0 or lengths.shape[1] == 0 or permute.size == 0:
+        return lengths.copy(), values.copy(), None if weights is None else weights.copy()
+    seg = lengths.astype(np.int64).sum(axis=1)
+    off = np.zeros(seg.size + 1, dtype=np.int64)
+    off[1:] = np.cumsum(seg)
+    rows = [int(r) for r in permute]
+    out_v = np.concatenate([values[off[r]:off[r + 1]] for r in rows]) if rows else values[:0]
+    out_w = None
+    if weights is not None:
+        out_w = np.concatenate([weights[off[r]:off[r + 1]] for r in rows], axis=0)
+    return lengths[np.asarray(rows, dtype=np.int64)], out_v, out_w
