@@ -41,6 +41,8 @@ EXPORTS = {
                                                     _vp, _vp]),
     "tbe_b200_complete_cumsum_scratch_bytes": (_i64, [_i64]),
     "tbe_b200_complete_cumsum": (_i32, [_vp, _i64, _i32, _vp, _vp, _i64, _vp]),
+    "tbe_b200_complete_cumsum_static_max_elements": (_i64, []),
+    "tbe_b200_complete_cumsum_static": (_i32, [_vp, _i64, _i32, _vp, _vp]),
     "tbe_b200_permute_2d_sparse_scratch_bytes": (_i64, [_i64, _i64]),
     "tbe_b200_permute_2d_sparse_offsets": (_i32, [_vp, _i64, _vp, _i32, _i64, _i64, _vp, _vp, _i64, _vp, _vp]),
     "tbe_b200_permute_2d_sparse_copy": (_i32, [_vp, _i64, _i64, _vp, _i64, _vp, _i64, _vp, _vp, _i64, _vp, _vp]),

@@ -11,6 +11,8 @@
 //
 // Both are streaming integer work bounded by HBM bandwidth.  Both need a little global memory beyond
 // their inputs and outputs (per-tile sums; per-table segment lengths and offsets): the caller passes it.
+#include <mutex>
+
 #include "tbe_common.cuh"
 
 namespace tbe {
@@ -346,4 +348,69 @@ extern "C" int tbe_b200_permute_2d_sparse_copy(const int32_t* permute, int64_t T
     if (rc != TBE_B200_OK) return rc;
     if (weights) rc = copy_segments(weights, out_weights, weight_row_bytes, out_capacity, permute, T_in, T_out, in_off, out_off, s);
     return rc;
+}
+
+// ---- complete cumsum for callers that must not allocate ---------------------------------------
+//
+// The tile sums live in a fixed array inside the library image instead of caller-provided scratch.
+// Every GPU that loads the library carries these 64 KB until the process ends.
+
+namespace tbe {
+namespace {
+
+constexpr int64_t kStaticTiles = 8192;                               // 8192 tile sums = 64 KB
+constexpr int64_t kStaticMaxElements = kStaticTiles * kScanTile;     // 16 777 216 input elements
+constexpr int kCachedDevices = 64;
+
+static __device__ __align__(256) int64_t g_static_tile_sums[kStaticTiles];
+
+// Device address of the array on the current device.  In host code `g_static_tile_sums` is only a handle
+// for the runtime, never a pointer a kernel may use; the address is looked up once per device and kept.
+int static_tile_sums(int64_t** out)
+{
+    static std::mutex lock;
+    static int64_t* cached[kCachedDevices] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return fail(TBE_B200_ERR_CUDA, "complete_cumsum_static: no current device");
+    std::lock_guard<std::mutex> g(lock);
+    if (dev >= 0 && dev < kCachedDevices && cached[dev]) {
+        *out = cached[dev];
+        return TBE_B200_OK;
+    }
+    void* p = nullptr;
+    const cudaError_t e = cudaGetSymbolAddress(&p, g_static_tile_sums);
+    if (e != cudaSuccess || !p)
+        return fail(TBE_B200_ERR_CUDA, "complete_cumsum_static: the scratch array has no address on device %d (%s)", dev, cudaGetErrorString(e));
+    if (dev >= 0 && dev < kCachedDevices) cached[dev] = static_cast<int64_t*>(p);
+    *out = static_cast<int64_t*>(p);
+    return TBE_B200_OK;
+}
+
+}  // namespace
+}  // namespace tbe
+
+extern "C" int64_t tbe_b200_complete_cumsum_static_max_elements(void) { return tbe::kStaticMaxElements; }
+
+extern "C" int tbe_b200_complete_cumsum_static(const void* in, int64_t n, int index_bits, void* out, tbe_b200_stream_t stream)
+{
+    using namespace tbe;
+    if (n < 0) return fail(TBE_B200_ERR_INVALID_ARGUMENT, "complete_cumsum_static: n must be non-negative");
+    if (index_bits != 32 && index_bits != 64)
+        return fail(TBE_B200_ERR_INVALID_ARGUMENT, "complete_cumsum_static: index_bits must be 32 or 64, got %d", index_bits);
+    if (!out || (n > 0 && !in)) return fail(TBE_B200_ERR_INVALID_ARGUMENT, "complete_cumsum_static: a required pointer is NULL");
+    if (n > kStaticMaxElements)
+        return fail(TBE_B200_ERR_UNSUPPORTED,
+                    "complete_cumsum_static: %lld elements exceed the built-in scratch (at most %lld); use tbe_b200_complete_cumsum "
+                    "with caller-provided scratch",
+                    static_cast<long long>(n), static_cast<long long>(kStaticMaxElements));
+    cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+    if (n == 0) {
+        if (cudaMemsetAsync(out, 0, index_bits / 8, s) != cudaSuccess) return fail(TBE_B200_ERR_CUDA, "complete_cumsum_static: memset failed");
+        return TBE_B200_OK;
+    }
+    int64_t* tile_sums = nullptr;
+    const int rc = static_tile_sums(&tile_sums);
+    if (rc != TBE_B200_OK) return rc;
+    // Every tile sum the scan reads is written by the first kernel of this call, so nothing has to be cleared.
+    return complete_cumsum_launch(in, n, index_bits, out, tile_sums, s);
 }

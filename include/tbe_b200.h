@@ -187,6 +187,23 @@ int64_t tbe_b200_complete_cumsum_scratch_bytes(int64_t n);
 int tbe_b200_complete_cumsum(const void* in, int64_t n, int index_bits, void* out, void* scratch, int64_t scratch_bytes,
                              tbe_b200_stream_t stream);
 
+/* Complete cumulative sum that allocates nothing and takes no scratch from the caller.  It has no counterpart
+ * in the reference.  It exists for hosts that cannot hand the library any extra device memory at call time:
+ * a serving process that reserved the whole GPU for its tables at start-up and never calls the CUDA allocator
+ * again (an allocation there can fail, or stall every stream of the device while it runs), or a runtime whose
+ * memory arena is owned by another component.  The per-tile sums go into a 64 KB array that is part of the
+ * library image; every GPU that loads the library holds those 64 KB until the process exits.
+ *   - n may be at most tbe_b200_complete_cumsum_static_max_elements() (16 777 216); a longer input is refused
+ *     with TBE_B200_ERR_UNSUPPORTED and a message that names the limit.
+ *   - The first call on each device looks the array's device address up once, with that device current; make
+ *     that first call outside any stream capture.
+ *   - All calls on a device share the one array and it keeps what the last call left there.  Nothing in it has
+ *     to start at zero, but two calls whose kernels can run at the same time (different streams, no ordering
+ *     between them) race on it: order them, or give one of them tbe_b200_complete_cumsum with its own scratch.
+ * Same result as tbe_b200_complete_cumsum, bit for bit. */
+int64_t tbe_b200_complete_cumsum_static_max_elements(void);
+int tbe_b200_complete_cumsum_static(const void* in, int64_t n, int index_bits, void* out, tbe_b200_stream_t stream);
+
 /* Reordering of a jagged request by table; replaces aclnnPermute2dSparseData, reached from
  * permute2d_sparse_data_impl_npu (src/sparse_ops/permute2d_sparse_data/permute2d_sparse_data.cpp:45-150) and, with
  * B = 1, permute1d_sparse_data_impl_npu (permute1d_sparse_data.cpp:81-165).  `lengths` is [T_in, B] (int32 or
