@@ -28,6 +28,10 @@ import time
 import torch
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
+
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant kernel, from the ncu captures
+# summarised under profiles/ (workload, scale_e, scale_b) -> bytes
+NCU_TRAFFIC_BYTES = {("c2", 1.0, 1.0): 155_366_912 + 33_108_992}
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
@@ -293,7 +297,9 @@ def run_single_gpu(args):
                                 "batches rotate, so hot rows stay L2-resident as in steady-state serving",
                    "build_s": round(t_build, 1)},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "traffic": None, "peak_kind": peak_kind, "kernel": "tbe_pooled_kernel",
+                     "traffic": NCU_TRAFFIC_BYTES.get((name, args.scale_e, args.scale_b)), "traffic_source": "ncu capture of one "
+                     "launch of this workload (profiles/tbe_pooled_kernel_c2.md); null for workloads not captured",
+                     "peak_kind": peak_kind, "kernel": "tbe_pooled_kernel",
                      "kernel_ms": kern_ms, "algorithmic_bytes_per_launch": alg_bytes,
                      "padded_bytes_per_launch": statistics.mean(a["padded"] for a in acct),
                      "sector_bytes_per_launch": statistics.mean(a["sector"] for a in acct),

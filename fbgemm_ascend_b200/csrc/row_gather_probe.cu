@@ -11,7 +11,8 @@
 //   bulk  one cp.async.bulk per row (one row per lane, 32 rows per warp in flight) into shared memory,
 //         completion on an mbarrier, rows read back with 16-byte shared loads
 // Row ids are drawn once into a device array (uniform, or bounded Zipf scattered by a multiplicative
-// permutation, per table) and streamed by the gather kernels, as the lookup streams `indices`.
+// permutation, per table; samples are table-major like the lookup's bags) and streamed by the gather
+// kernels, as the lookup streams `indices`.
 //
 // Usage: tbe_b200_row_gather_probe [max_gib]      (tables larger than max_gib GiB are skipped; default 120)
 // Output: one line per (distribution, stride, method): rows/s and the bytes/s they stand for.
@@ -42,14 +43,16 @@ __device__ __forceinline__ uint32_t hash32(uint32_t x)
     return x;
 }
 
-// Row id of sample s: table = hash % T; rank ~ bounded Zipf(alpha) over N rows (alpha == 0: uniform);
+// Row id of sample s: table = s * T / n; rank ~ bounded Zipf(alpha) over N rows (alpha == 0: uniform);
 // rank -> row by an odd multiplier modulo N, so hot rows are scattered.
 __global__ void draw_rows(uint32_t* rows, uint64_t n, uint32_t T, uint32_t N, float alpha, float c /* N^(1-alpha) - 1 */)
 {
     const uint64_t s = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
     if (s >= n) return;
     const uint32_t h = hash32(static_cast<uint32_t>(s) * 2654435761u + 12345u);
-    const uint32_t t = static_cast<uint32_t>((static_cast<uint64_t>(hash32(h ^ 0x9e3779b9u)) * T) >> 32);
+    // Table-major, like the lookup's bag order: the warps that run at the same time work on the same one or
+    // two tables, so the live footprint is a table, not the whole shard.
+    const uint32_t t = static_cast<uint32_t>(s * T / n);
     uint32_t r;
     if (alpha == 0.0f) {
         r = static_cast<uint32_t>((static_cast<uint64_t>(h) * N) >> 32);
@@ -69,10 +72,13 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) gather_ldg(const uint8_t*
     constexpr int UNR = 4;
     const int lane = threadIdx.x & 31, k = lane & 7, g = lane >> 3;
     const uint64_t gw = static_cast<uint64_t>(blockIdx.x) * kWarpsPerBlock + (threadIdx.x >> 5);
-    const uint32_t* mine = rows + gw * rows_per_warp;
+    // Round r of every warp reads one contiguous stretch of the sample array, so all warps move through the
+    // tables together, as the blocks of the lookup kernel do.
+    const uint64_t round_pitch = static_cast<uint64_t>(gridDim.x) * kWarpsPerBlock * 32;
+    const uint32_t* mine = rows + gw * 32;
     uint32_t acc = 0;
     for (uint32_t r = 0; r < rows_per_warp; r += 32) {
-        const uint32_t my_row = __ldg(mine + r + lane);
+        const uint32_t my_row = __ldg(mine + (r / 32) * round_pitch + lane);
         for (int u0 = 0; u0 < 8; u0 += UNR) {
             uint4 v[UNR];
             uint32_t t[UNR];
@@ -103,7 +109,8 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) gather_bulk(const uint8_t
     __shared__ __align__(8) uint64_t bars[kWarpsPerBlock];
     const int lane = threadIdx.x & 31, k = lane & 7, g = lane >> 3, warp = threadIdx.x >> 5;
     const uint64_t gw = static_cast<uint64_t>(blockIdx.x) * kWarpsPerBlock + warp;
-    const uint32_t* mine = rows + gw * rows_per_warp;
+    const uint64_t round_pitch = static_cast<uint64_t>(gridDim.x) * kWarpsPerBlock * 32;
+    const uint32_t* mine = rows + gw * 32;
     const uint32_t bar = s32(&bars[warp]);
     const uint32_t base = s32(smem) + warp * 32 * stride;
     if (lane == 0) {
@@ -113,7 +120,7 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) gather_bulk(const uint8_t
     __syncwarp();
     uint32_t acc = 0, parity = 0;
     for (uint32_t r = 0; r < rows_per_warp; r += 32) {
-        const uint8_t* src = table + static_cast<uint64_t>(__ldg(mine + r + lane)) * stride;
+        const uint8_t* src = table + static_cast<uint64_t>(__ldg(mine + (r / 32) * round_pitch + lane)) * stride;
         __syncwarp();
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(stride) : "memory");

@@ -659,8 +659,6 @@ __device__ __forceinline__ TableMeta load_meta(const LookupParams& p, int t)
     return m;
 }
 
-__device__ __forceinline__ void prefetch_l2(const void* p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
-
 // ---- byte-wise path (any alignment, any D, every type) ----------------------
 
 __device__ __forceinline__ float decode_elem(const uint8_t* row, int ty, int e, float scale, float bias,
@@ -782,6 +780,55 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity)
         if (done) return true;
     }
     return false;
+}
+
+// Adds one INT8 / INT4 row chunk to a lane's 16 slots.  `w0` is the lane's first payload word (the row's tail
+// on the header lane), words[1..] the rest of its chunk, `hdr` the row header (fp16 scale, fp16 bias; zero
+// for a row that is not to be added).
+template <int TY, bool WEIGHTED, bool FOLD>
+__device__ __forceinline__ void accum_header_row(uint32_t w0, const uint32_t (&words)[4], uint32_t hdr, float w, float (&acc)[16],
+                                                 float& bias_acc, float& scale_acc)
+{
+    constexpr bool k8 = (TY == TBE_B200_INT8);
+    const unsigned short scale_h = static_cast<unsigned short>(hdr & 0xffffu);
+    float ws = 0.0f;
+    if constexpr (WEIGHTED) {
+        ws = half_bits_to_float(scale_h) * w;
+        bias_acc = fmaf(half_bits_to_float(hdr >> 16), w, bias_acc);
+    } else {
+        bias_acc += half_bits_to_float(hdr >> 16);
+        if constexpr (FOLD) scale_acc += half_bits_to_float(scale_h);
+    }
+    if (k8) {
+#pragma unroll
+        for (int i4 = 0; i4 < 4; ++i4) {
+            const uint32_t c = (i4 == 0) ? w0 : words[i4];
+            // bytes 0 and 2, then bytes 1 and 3, placed in the mantissas of half2(1024, 1024)
+            uint32_t even = (c & 0x00FF00FFu) | 0x64006400u;
+            uint32_t odd = __byte_perm(c, 0x64646464u, 0x4341);
+            if constexpr (!FOLD) {
+                even = codes_to_half2(even, 0x64006400u);
+                odd = codes_to_half2(odd, 0x64006400u);
+            }
+            add_pair_t<WEIGHTED>(acc[4 * i4 + 0], acc[4 * i4 + 2], even, scale_h, ws);
+            add_pair_t<WEIGHTED>(acc[4 * i4 + 1], acc[4 * i4 + 3], odd, scale_h, ws);
+        }
+    } else {
+#pragma unroll
+        for (int i2 = 0; i2 < 2; ++i2) {
+            const uint32_t c = (i2 == 0) ? w0 : words[i2];
+            const uint32_t y = c >> 8;
+            // nibble pairs (j, j + 4) sit 16 bits apart: 0x6400 | n = 1024 + n; 0x5400 | (n << 4) = 64 + n
+            const uint32_t p0 = codes_to_half2((c & 0x000F000Fu) | 0x64006400u, 0x64006400u);   // nibbles 0, 4
+            const uint32_t p1 = codes_to_half2((c & 0x00F000F0u) | 0x54005400u, 0x54005400u);   // nibbles 1, 5
+            const uint32_t p2 = codes_to_half2((y & 0x000F000Fu) | 0x64006400u, 0x64006400u);   // nibbles 2, 6
+            const uint32_t p3 = codes_to_half2((y & 0x00F000F0u) | 0x54005400u, 0x54005400u);   // nibbles 3, 7
+            add_pair_t<WEIGHTED>(acc[8 * i2 + 0], acc[8 * i2 + 4], p0, scale_h, ws);
+            add_pair_t<WEIGHTED>(acc[8 * i2 + 1], acc[8 * i2 + 5], p1, scale_h, ws);
+            add_pair_t<WEIGHTED>(acc[8 * i2 + 2], acc[8 * i2 + 6], p2, scale_h, ws);
+            add_pair_t<WEIGHTED>(acc[8 * i2 + 3], acc[8 * i2 + 7], p3, scale_h, ws);
+        }
+    }
 }
 
 // Output address of element 0 of bag `b` of the table at column `col`, when the result is scattered
@@ -1000,45 +1047,7 @@ __device__ __noinline__ bool pool_run_staged(const LookupParams& p, const TableM
                     const uint32_t x = lds4(ex);
                     const uint32_t hdr = head_lane ? words[0] : x;
                     const uint32_t w0 = head_lane ? x : words[0];
-                    const unsigned short scale_h = static_cast<unsigned short>(hdr & 0xffffu);
-                    float ws = 0.0f;
-                    if constexpr (WEIGHTED) {
-                        ws = half_bits_to_float(scale_h) * w;
-                        bias_acc = fmaf(half_bits_to_float(hdr >> 16), w, bias_acc);
-                    } else {
-                        bias_acc += half_bits_to_float(hdr >> 16);
-                        if constexpr (FOLD) scale_acc += half_bits_to_float(scale_h);
-                    }
-                    if (k8) {
-#pragma unroll
-                        for (int i4 = 0; i4 < 4; ++i4) {
-                            const uint32_t c = (i4 == 0) ? w0 : words[i4];
-                            // bytes 0 and 2, then bytes 1 and 3, placed in the mantissas of half2(1024, 1024)
-                            uint32_t even = (c & 0x00FF00FFu) | 0x64006400u;
-                            uint32_t odd = __byte_perm(c, 0x64646464u, 0x4341);
-                            if constexpr (!FOLD) {
-                                even = codes_to_half2(even, 0x64006400u);
-                                odd = codes_to_half2(odd, 0x64006400u);
-                            }
-                            add_pair_t<WEIGHTED>(acc[4 * i4 + 0], acc[4 * i4 + 2], even, scale_h, ws);
-                            add_pair_t<WEIGHTED>(acc[4 * i4 + 1], acc[4 * i4 + 3], odd, scale_h, ws);
-                        }
-                    } else {
-#pragma unroll
-                        for (int i2 = 0; i2 < 2; ++i2) {
-                            const uint32_t c = (i2 == 0) ? w0 : words[i2];
-                            const uint32_t y = c >> 8;
-                            // nibble pairs (j, j + 4) sit 16 bits apart: 0x6400 | n = 1024 + n; 0x5400 | (n << 4) = 64 + n
-                            const uint32_t p0 = codes_to_half2((c & 0x000F000Fu) | 0x64006400u, 0x64006400u);   // nibbles 0, 4
-                            const uint32_t p1 = codes_to_half2((c & 0x00F000F0u) | 0x54005400u, 0x54005400u);   // nibbles 1, 5
-                            const uint32_t p2 = codes_to_half2((y & 0x000F000Fu) | 0x64006400u, 0x64006400u);   // nibbles 2, 6
-                            const uint32_t p3 = codes_to_half2((y & 0x00F000F0u) | 0x54005400u, 0x54005400u);   // nibbles 3, 7
-                            add_pair_t<WEIGHTED>(acc[8 * i2 + 0], acc[8 * i2 + 4], p0, scale_h, ws);
-                            add_pair_t<WEIGHTED>(acc[8 * i2 + 1], acc[8 * i2 + 5], p1, scale_h, ws);
-                            add_pair_t<WEIGHTED>(acc[8 * i2 + 2], acc[8 * i2 + 6], p2, scale_h, ws);
-                            add_pair_t<WEIGHTED>(acc[8 * i2 + 3], acc[8 * i2 + 7], p3, scale_h, ws);
-                        }
-                    }
+                    accum_header_row<TY, WEIGHTED, FOLD>(w0, words, hdr, w, acc, bias_acc, scale_acc);
                 } else if constexpr (TY == TBE_B200_FP8) {
                     // byte -> fp32 by bit placement: ((b & 0x7f) << (16 + ebits)) as a float, times 2^(127 - bias),
                     // sign bit or'ed in (reference: c310/op_kernel/common.h:120-167)

@@ -102,8 +102,10 @@ typedef struct {
     const int64_t* output_col_offsets;  /* [T] or NULL (pooled modes) */
     void* const* dest_outputs;          /* [ceil(B / rows_per_dest)] device array of base pointers, or NULL */
     int64_t rows_per_dest;              /* used only with dest_outputs */
-    int32_t* error_flag;                /* optional device word: or'ed with 1 when an index < -1 is met
-                                           (that row is skipped); NULL = no reporting */
+    int32_t* error_flag;                /* optional device word: or'ed with 1 when an index outside [-1, 2^31) is
+                                           met (that row is skipped), with 2 when a warp gave up waiting for rows
+                                           it had requested (its remaining bags are left unwritten; the wait is
+                                           bounded so that the kernel always ends); NULL = no reporting */
 } tbe_b200_lookup_args;
 
 /* Pooled (SUM / MEAN) or sequence (NONE) lookup over fused INT8 / INT4 / INT2 /
