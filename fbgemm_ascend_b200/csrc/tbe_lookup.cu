@@ -1111,33 +1111,33 @@ __device__ __noinline__ bool pool_run_staged(const LookupParams& p, const TableM
             const int64_t bag = j + g;
             char* seg = p.dests ? dest_segment(p, b0 + bag, m.col, esz) : out_run + bag * row_bytes;
             const bool vec = p.dests ? (reinterpret_cast<uintptr_t>(seg) & 15) == 0 : vec_ok;
-            if (kHdr && p.out_ty != TBE_B200_FP32 && vec) {
-                // 16-bit output of INT8 / INT4 rows: a lane's 16 elements start HS elements before a 32-byte
-                // boundary.  Its first HS elements go to the lane below (the header lane's, the row's tail, to
-                // the last lane), after which every lane owns elements [16k, 16k + 16): two aligned 16-byte
-                // stores, whole sectors, instead of four 8-byte ones that share sectors with the neighbours.
-                uint32_t h[8];
+            bool stored = false;
+            if constexpr (FOLD) {
+                // Unweighted INT8 with a 16-bit output (the only instantiation that carries this code: compiled into
+                // the others it cost the INT4 and fp32-output shapes 4 % through register allocation alone).  A
+                // lane's 16 elements start 4 elements before a 32-byte boundary.  Its first 4 go to the lane below
+                // (the header lane's, the row's tail, to the last lane), after which every lane owns elements
+                // [16k, 16k + 16): two aligned 16-byte stores, whole sectors, instead of four 8-byte ones that share
+                // sectors with the neighbours.
+                if (vec) {
+                    uint32_t h[8];
 #pragma unroll
-                for (int q = 0; q < 8; ++q) {
-                    const float lo16 = (acc[2 * q] + bias_acc) * mean_mul, hi16 = (acc[2 * q + 1] + bias_acc) * mean_mul;
-                    h[q] = (p.out_ty == TBE_B200_FP16) ? (f32_to_f16_bits(lo16) | (f32_to_f16_bits(hi16) << 16))
-                                                       : (f32_to_bf16_bits(lo16) | (f32_to_bf16_bits(hi16) << 16));
-                }
-                const int from = (k + 1 == nunits) ? 0 : k + 1;
-                uint32_t up[HS / 2 > 0 ? HS / 2 : 1];
-#pragma unroll
-                for (int q = 0; q < HS / 2; ++q) up[q] = __shfl_sync(kFull, h[q], from, LPR);
-                if (active && bag < nb) {
-                    char* dst = seg + 32 * k;
-                    if constexpr (HS == 4) {
-                        st_stream16(dst, make_uint4(h[2], h[3], h[4], h[5]));
-                        st_stream16(dst + 16, make_uint4(h[6], h[7], up[0], up[1]));
-                    } else {
-                        st_stream16(dst, make_uint4(h[4], h[5], h[6], h[7]));
-                        st_stream16(dst + 16, make_uint4(up[0], up[1], up[2], up[3]));
+                    for (int q = 0; q < 8; ++q) {
+                        const float lo16 = (acc[2 * q] + bias_acc) * mean_mul, hi16 = (acc[2 * q + 1] + bias_acc) * mean_mul;
+                        h[q] = (p.out_ty == TBE_B200_FP16) ? (f32_to_f16_bits(lo16) | (f32_to_f16_bits(hi16) << 16))
+                                                           : (f32_to_bf16_bits(lo16) | (f32_to_bf16_bits(hi16) << 16));
                     }
+                    const int from = (k + 1 == nunits) ? 0 : k + 1;
+                    const uint32_t up0 = __shfl_sync(kFull, h[0], from, LPR);
+                    const uint32_t up1 = __shfl_sync(kFull, h[1], from, LPR);
+                    if (active && bag < nb) {
+                        st_stream16(seg + 32 * k, make_uint4(h[2], h[3], h[4], h[5]));
+                        st_stream16(seg + 32 * k + 16, make_uint4(h[6], h[7], up0, up1));
+                    }
+                    stored = true;
                 }
-            } else if (active && bag < nb) {
+            }
+            if (!stored && active && bag < nb) {
 #pragma unroll
                 for (int q = 0; q < 4; ++q) {
                     float v[4];
@@ -1278,6 +1278,12 @@ tbe_pooled_kernel(const __grid_constant__ LookupParams p)
     const int64_t span_lo = gw * p.span;
     const int64_t span_hi = min(p.num_bags, span_lo + p.span);
     if (span_lo >= span_hi) return;
+    // The span's first offsets are needed right after the table description: ask for their line(s) now, so the two
+    // latencies overlap.
+    if (lane < 2) {
+        const IdxT* o = static_cast<const IdxT*>(p.offsets) + (lane == 0 ? span_lo : span_hi);
+        asm volatile("prefetch.global.L1 [%0];" ::"l"(o));
+    }
     // One mbarrier per warp; every lane arrives once per round of staged rows.
     if (lane == 0) mbar_init(bar, kWarp);
     __syncwarp();
