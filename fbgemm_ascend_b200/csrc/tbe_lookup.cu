@@ -1031,7 +1031,7 @@ __device__ __noinline__ bool pool_run_staged(const LookupParams& p, const TableM
 
             const int cnt = min(R, maxn - r * R);
             uint32_t rd = read0, ex = extra0;
-#pragma unroll 2
+#pragma unroll 1
             for (int u = 0; u < cnt; ++u, rd += pass_pitch, ex += pass_pitch) {
                 float w = 1.0f;
                 if constexpr (WEIGHTED) w = __shfl_sync(kFull, w_cur, u, LPR);
