@@ -1324,41 +1324,202 @@ tbe_pooled_kernel(const __grid_constant__ LookupParams p)
     }
 }
 
-// Pooling NONE: one warp per position n of `indices`; row n of the output gets the
-// dequantised row, zero-filled from D_t up to max_D.  Table of position n: the t with offsets[t*B] <= n < offsets[(t+1)*B].
+// ---- pooling NONE (sequence mode) --------------------------------------------------------------
+//
+// Row n of the output gets the dequantised row indices[n] of the table that position n belongs to (the t with
+// offsets[t*B] <= n < offsets[(t+1)*B]), zero-filled from D_t up to max_D.  A warp takes kNobagChunk consecutive
+// positions: the table is found once by binary search and then followed, and G = 32 / LPR rows are handled per
+// pass, LPR lanes per row, 16 elements per lane, with the same chunk-to-element mapping as the pooled path.
+// Nothing is accumulated, so rows go straight to registers; value = code * scale + bias in one mixed FMA.
+
+constexpr int kNobagChunk = 64;
+
+// One position through the byte-wise decoder (any type, alignment and width).
+template <typename IdxT>
+__device__ __noinline__ void nobag_position_bytewise(const LookupParams& p, const TableMeta& m, const IdxT* indices, int64_t n, int max_D,
+                                                     int lane)
+{
+    const int esz = (p.out_ty == TBE_B200_FP32) ? 4 : 2;
+    void* seg = static_cast<char*>(p.output) + n * p.out_stride * esz;
+    const int64_t idx = static_cast<int64_t>(indices[n]);
+    if (idx < 0) {
+        if (idx < -1 && lane == 0 && p.error_flag) atomicOr(p.error_flag, 1);
+        for (int e = lane; e < max(m.D, max_D); e += kWarp) store_scalar(seg, e, 0.0f, p.out_ty);
+        return;
+    }
+    const uint8_t* row = m.table + idx * m.stride;
+    float scale, bias;
+    read_header(row, m.ty, scale, bias);
+    for (int e = lane; e < m.D; e += kWarp)
+        store_scalar(seg, e, decode_elem(row, m.ty, e, scale, bias, p.fp8_shift, p.fp8_mult), p.out_ty);
+    for (int e = m.D + lane; e < max_D; e += kWarp) store_scalar(seg, e, 0.0f, p.out_ty);
+}
+
+// `cnt` consecutive positions [n, n + cnt) of one table with aligned rows of D = 16 * units <= 512 elements.
+template <int TY, int LPR, typename IdxT>
+__device__ __forceinline__ void nobag_rows(const LookupParams& p, const TableMeta& m, const IdxT* indices, int64_t n, int cnt, int max_D,
+                                           int lane)
+{
+    constexpr bool kHdr = (TY == TBE_B200_INT8 || TY == TBE_B200_INT4);
+    constexpr bool k8 = (TY == TBE_B200_INT8);
+    constexpr int CH = (TY == TBE_B200_INT4) ? 8 : 16;
+    constexpr int NCH = (TY == TBE_B200_FP16) ? 2 : (TY == TBE_B200_FP32) ? 4 : 1;
+    constexpr int EPC = 16 / NCH;
+    constexpr int HS = k8 ? 4 : (TY == TBE_B200_INT4 ? 8 : 0);
+    constexpr int G = kWarp / LPR;
+    const int k = lane % LPR, g = lane / LPR;
+    const int D = m.D, nunits = D / 16;
+    const bool head_lane = kHdr && k == 0;
+    const bool active = k < nunits;
+    const int esz = (p.out_ty == TBE_B200_FP32) ? 4 : 2;
+    for (int r0 = 0; r0 < cnt; r0 += G) {
+        const bool mine = r0 + g < cnt;
+        int64_t idx = -1;
+        if (mine) {
+            idx = static_cast<int64_t>(__ldg(indices + n + r0 + g));
+            if ((idx < -1 || idx > 0x7fffffffll) && k == 0 && p.error_flag) atomicOr(p.error_flag, 1);
+            if (idx > 0x7fffffffll) idx = -1;
+        }
+        const bool ok = idx >= 0;
+        const uint8_t* row = m.table + (ok ? idx : 0) * m.stride;
+        uint32_t words[4 * NCH];
+#pragma unroll
+        for (int c = 0; c < 4 * NCH; ++c) words[c] = 0u;
+        uint32_t tail = 0u;
+        if (ok && active) {
+            if constexpr (TY == TBE_B200_INT4) {
+                const uint2 v = ldg8(row + k * 8);
+                words[0] = v.x; words[1] = v.y;
+            } else {
+#pragma unroll
+                for (int c = 0; c < NCH; ++c) {
+                    const uint4 v = ldg16(row + 16 * (k + c * nunits));
+                    words[4 * c + 0] = v.x; words[4 * c + 1] = v.y; words[4 * c + 2] = v.z; words[4 * c + 3] = v.w;
+                }
+            }
+            if (head_lane) tail = ldg4(row + (k8 ? D : D / 2));
+        }
+        float v[16];
+        if constexpr (kHdr) {
+            const uint32_t hdr = __shfl_sync(kFull, words[0], 0, LPR);   // zero for a row that is not read
+            const uint32_t w0 = head_lane ? tail : words[0];
+            const unsigned short scale_h = static_cast<unsigned short>(hdr & 0xffffu);
+            const float bias = half_bits_to_float(hdr >> 16);
+#pragma unroll
+            for (int s = 0; s < 16; ++s) v[s] = bias;
+            if (k8) {
+#pragma unroll
+                for (int i4 = 0; i4 < 4; ++i4) {
+                    const uint32_t c = (i4 == 0) ? w0 : words[i4];
+                    const uint32_t even = codes_to_half2((c & 0x00FF00FFu) | 0x64006400u, 0x64006400u);
+                    const uint32_t odd = codes_to_half2(__byte_perm(c, 0x64646464u, 0x4341), 0x64006400u);
+                    add_pair_t<false>(v[4 * i4 + 0], v[4 * i4 + 2], even, scale_h, 0.0f);
+                    add_pair_t<false>(v[4 * i4 + 1], v[4 * i4 + 3], odd, scale_h, 0.0f);
+                }
+            } else {
+#pragma unroll
+                for (int i2 = 0; i2 < 2; ++i2) {
+                    const uint32_t c = (i2 == 0) ? w0 : words[i2];
+                    const uint32_t y = c >> 8;
+                    const uint32_t p0 = codes_to_half2((c & 0x000F000Fu) | 0x64006400u, 0x64006400u);
+                    const uint32_t p1 = codes_to_half2((c & 0x00F000F0u) | 0x54005400u, 0x54005400u);
+                    const uint32_t p2 = codes_to_half2((y & 0x000F000Fu) | 0x64006400u, 0x64006400u);
+                    const uint32_t p3 = codes_to_half2((y & 0x00F000F0u) | 0x54005400u, 0x54005400u);
+                    add_pair_t<false>(v[8 * i2 + 0], v[8 * i2 + 4], p0, scale_h, 0.0f);
+                    add_pair_t<false>(v[8 * i2 + 1], v[8 * i2 + 5], p1, scale_h, 0.0f);
+                    add_pair_t<false>(v[8 * i2 + 2], v[8 * i2 + 6], p2, scale_h, 0.0f);
+                    add_pair_t<false>(v[8 * i2 + 3], v[8 * i2 + 7], p3, scale_h, 0.0f);
+                }
+            }
+        } else if constexpr (TY == TBE_B200_FP8) {
+#pragma unroll
+            for (int s = 0; s < 16; ++s) {
+                const uint32_t by = (words[s >> 2] >> (8 * (s & 3))) & 0xffu;
+                const float mag = __uint_as_float((by & 0x7fu) << p.fp8_shift) * p.fp8_mult;
+                v[s] = __uint_as_float(__float_as_uint(mag) | ((by & 0x80u) << 24));
+            }
+        } else if constexpr (TY == TBE_B200_FP16) {
+#pragma unroll
+            for (int s = 0; s < 16; ++s) v[s] = half_bits_to_float((words[s >> 1] >> (16 * (s & 1))) & 0xffffu);
+        } else {
+#pragma unroll
+            for (int s = 0; s < 16; ++s) v[s] = __uint_as_float(words[s]);
+        }
+        if (mine) {
+            char* seg = static_cast<char*>(p.output) + (n + r0 + g) * p.out_stride * esz;
+            const bool vec = ((reinterpret_cast<uintptr_t>(seg)) & 15) == 0;
+            if (active) {
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const int slot = 4 * q;
+                    int e0;
+                    if constexpr (kHdr) e0 = (head_lane && slot < HS) ? (D - HS + slot) : (16 * k - HS + slot);
+                    else e0 = EPC * (k + (slot / EPC) * nunits) + (slot % EPC);
+                    store_out<4>(seg, e0, &v[slot], p.out_ty, vec);
+                }
+            }
+            for (int e = D + k; e < max_D; e += LPR) store_scalar(seg, e, 0.0f, p.out_ty);
+        }
+    }
+}
+
+template <int TY, typename IdxT>
+__device__ __forceinline__ void nobag_rows_by_width(const LookupParams& p, const TableMeta& m, const IdxT* indices, int64_t n, int cnt,
+                                                    int max_D, int lane)
+{
+    const int nunits = m.D / 16;
+    if (nunits <= 4) nobag_rows<TY, 4, IdxT>(p, m, indices, n, cnt, max_D, lane);
+    else if (nunits <= 8) nobag_rows<TY, 8, IdxT>(p, m, indices, n, cnt, max_D, lane);
+    else if (nunits <= 16) nobag_rows<TY, 16, IdxT>(p, m, indices, n, cnt, max_D, lane);
+    else nobag_rows<TY, 32, IdxT>(p, m, indices, n, cnt, max_D, lane);
+}
+
 template <typename IdxT>
 __global__ void __launch_bounds__(kWarpsPerBlock* kWarp)
-tbe_nobag_kernel(const LookupParams p, int64_t num_indices, int max_D)
+tbe_nobag_kernel(const __grid_constant__ LookupParams p, int64_t num_indices, int max_D)
 {
     const int lane = threadIdx.x & 31;
-    const int64_t n = static_cast<int64_t>(blockIdx.x) * kWarpsPerBlock + (threadIdx.x >> 5);
-    if (n >= num_indices) return;
+    const int64_t gw = static_cast<int64_t>(blockIdx.x) * kWarpsPerBlock + (threadIdx.x >> 5);
+    int64_t n = gw * kNobagChunk;
+    const int64_t n_end = min(num_indices, n + kNobagChunk);
+    if (n >= n_end) return;
     const IdxT* offsets = static_cast<const IdxT*>(p.offsets);
-    // Binary search over the T+1 table boundaries offsets[t*B].
+    const IdxT* indices = static_cast<const IdxT*>(p.indices);
+    // Binary search over the T+1 table boundaries offsets[t*B]: the table of the chunk's first position.
     int lo = 0, hi = p.T;   // invariant: boundary(lo) <= n < boundary(hi)
     while (hi - lo > 1) {
         const int mid = (lo + hi) >> 1;
         if (static_cast<int64_t>(offsets[static_cast<int64_t>(mid) * p.B]) <= n) lo = mid;
         else hi = mid;
     }
-    const int t = lo;
-    const int ty = p.weights_tys[t];
-    const int D = p.D_offsets[t + 1] - p.D_offsets[t];
-    const int esz = (p.out_ty == TBE_B200_FP32) ? 4 : 2;
-    void* seg = static_cast<char*>(p.output) + n * p.out_stride * esz;
-    const int64_t idx = static_cast<int64_t>(static_cast<const IdxT*>(p.indices)[n]);
-    if (idx < 0) {
-        if (idx < -1 && lane == 0 && p.error_flag) atomicOr(p.error_flag, 1);
-        for (int e = lane; e < max(D, max_D); e += kWarp) store_scalar(seg, e, 0.0f, p.out_ty);
-        return;
+    int t = lo;
+    while (n < n_end) {
+        // positions [n, stop) belong to table t (skip tables without positions)
+        int64_t stop = static_cast<int64_t>(offsets[static_cast<int64_t>(t + 1) * p.B]);
+        while (stop <= n && t + 1 < p.T) {
+            ++t;
+            stop = static_cast<int64_t>(offsets[static_cast<int64_t>(t + 1) * p.B]);
+        }
+        stop = (t + 1 >= p.T) ? n_end : min(stop, n_end);
+        if (stop <= n) stop = n_end;   // offsets that do not cover every position: the last table takes the rest
+        const TableMeta m = load_meta(p, t);
+        const int cnt = static_cast<int>(stop - n);
+        const bool fast = m.rows_aligned && m.D > 0 && (m.D & 15) == 0 && m.D <= 512;
+        bool done = fast;
+        if (fast) {
+            switch (m.ty) {
+                case TBE_B200_INT8: nobag_rows_by_width<TBE_B200_INT8, IdxT>(p, m, indices, n, cnt, max_D, lane); break;
+                case TBE_B200_INT4: nobag_rows_by_width<TBE_B200_INT4, IdxT>(p, m, indices, n, cnt, max_D, lane); break;
+                case TBE_B200_FP8: nobag_rows_by_width<TBE_B200_FP8, IdxT>(p, m, indices, n, cnt, max_D, lane); break;
+                case TBE_B200_FP16: nobag_rows_by_width<TBE_B200_FP16, IdxT>(p, m, indices, n, cnt, max_D, lane); break;
+                case TBE_B200_FP32: nobag_rows_by_width<TBE_B200_FP32, IdxT>(p, m, indices, n, cnt, max_D, lane); break;
+                default: done = false; break;
+            }
+        }
+        if (!done)
+            for (int64_t q = n; q < stop; ++q) nobag_position_bytewise<IdxT>(p, m, indices, q, max_D, lane);
+        n = stop;
     }
-    const int64_t stride = row_bytes_of(ty, D, p.row_alignment);
-    const uint8_t* row = p.dev_weights + p.weights_offsets[t] + idx * stride;
-    float scale, bias;
-    read_header(row, ty, scale, bias);
-    for (int e = lane; e < D; e += kWarp)
-        store_scalar(seg, e, decode_elem(row, ty, e, scale, bias, p.fp8_shift, p.fp8_mult), p.out_ty);
-    for (int e = D + lane; e < max_D; e += kWarp) store_scalar(seg, e, 0.0f, p.out_ty);
 }
 
 constexpr int kSpanLarge = 16;   // bags per warp when there is plenty of work; a multiple of every group count
@@ -1452,7 +1613,8 @@ extern "C" int tbe_b200_int_nbit_lookup(const tbe_b200_lookup_args* a, tbe_b200_
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
     if (a->pooling_mode == TBE_B200_POOL_NONE) {
         if (a->num_indices <= 0) return TBE_B200_OK;
-        const int64_t blocks = (a->num_indices + kWarpsPerBlock - 1) / kWarpsPerBlock;
+        const int64_t chunks = (a->num_indices + kNobagChunk - 1) / kNobagChunk;
+        const int64_t blocks = (chunks + kWarpsPerBlock - 1) / kWarpsPerBlock;
         if (blocks > 0x7fffffffll) return fail(TBE_B200_ERR_UNSUPPORTED, "lookup: too many indices for one launch");
         if (a->index_bits == 32)
             tbe_nobag_kernel<int32_t><<<static_cast<unsigned>(blocks), kWarpsPerBlock * kWarp, 0, s>>>(p, a->num_indices, a->max_D);
