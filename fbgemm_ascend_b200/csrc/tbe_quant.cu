@@ -130,6 +130,109 @@ quantize_8bit_kernel(const InT* __restrict__ in, int64_t N, int64_t D, uint8_t* 
     }
 }
 
+// The common 8-bit shapes, batched: fp32 rows of D = 4 * n <= 512 elements, 16-byte aligned.  A warp takes ROWS
+// rows at a time and keeps them in registers (VPL float4 per lane and row), so the loads of all ROWS rows are in
+// flight together and nothing is read twice; a fixed grid strides over the rows.  Same arithmetic as
+// quantize_8bit_kernel, hence the same bytes.
+template <bool TABLE, int VPL, int ROWS>
+__global__ void __launch_bounds__(kThreads)
+quantize_8bit_batched_kernel(const float* __restrict__ in, int64_t N, int64_t D, uint8_t* __restrict__ out, int64_t out_stride)
+{
+    const int lane = threadIdx.x & 31;
+    const int64_t nwarps = static_cast<int64_t>(gridDim.x) * (kThreads / 32);
+    const int64_t warp = static_cast<int64_t>(blockIdx.x) * (kThreads / 32) + (threadIdx.x >> 5);
+    const int nvec = static_cast<int>(D / 4);
+    const float4* in4 = reinterpret_cast<const float4*>(in);
+    for (int64_t r0 = warp * ROWS; r0 < N; r0 += nwarps * ROWS) {
+        float4 f[ROWS][VPL];
+#pragma unroll
+        for (int j = 0; j < ROWS; ++j)
+#pragma unroll
+            for (int v = 0; v < VPL; ++v)
+                if (r0 + j < N && lane + 32 * v < nvec) f[j][v] = __ldg(in4 + (r0 + j) * nvec + lane + 32 * v);
+#pragma unroll
+        for (int j = 0; j < ROWS; ++j) {
+            float mn = __int_as_float(0x7f800000), mx = __int_as_float(0xff800000);
+#pragma unroll
+            for (int v = 0; v < VPL; ++v)
+                if (r0 + j < N && lane + 32 * v < nvec) {
+                    mn = fminf(fminf(mn, f[j][v].x), fminf(f[j][v].y, fminf(f[j][v].z, f[j][v].w)));
+                    mx = fmaxf(fmaxf(mx, f[j][v].x), fmaxf(f[j][v].y, fmaxf(f[j][v].z, f[j][v].w)));
+                }
+            // whole-warp min / max in one instruction each (sm_100a reduces fp32 across the warp in hardware)
+            asm volatile("redux.sync.min.f32 %0, %0, 0xffffffff;" : "+f"(mn));
+            asm volatile("redux.sync.max.f32 %0, %0, 0xffffffff;" : "+f"(mx));
+            if (r0 + j >= N) continue;
+            const float range = mx - mn;
+            const float scale = __fdiv_rn(range, 255.0f);
+            const float inv = __fdiv_rn(255.0f, __fadd_rn(range, 1e-8f));
+            uint8_t* o = out + (r0 + j) * out_stride;
+            uint8_t* codes = TABLE ? o + 4 : o;
+#pragma unroll
+            for (int v = 0; v < VPL; ++v)
+                if (lane + 32 * v < nvec) {
+                    const float4 x = f[j][v];
+                    const uint32_t q0 = static_cast<uint32_t>(__float2int_rn(__fmul_rn(__fsub_rn(x.x, mn), inv))) & 0xffu;
+                    const uint32_t q1 = static_cast<uint32_t>(__float2int_rn(__fmul_rn(__fsub_rn(x.y, mn), inv))) & 0xffu;
+                    const uint32_t q2 = static_cast<uint32_t>(__float2int_rn(__fmul_rn(__fsub_rn(x.z, mn), inv))) & 0xffu;
+                    const uint32_t q3 = static_cast<uint32_t>(__float2int_rn(__fmul_rn(__fsub_rn(x.w, mn), inv))) & 0xffu;
+                    *reinterpret_cast<uint32_t*>(codes + 4 * (lane + 32 * v)) = q0 | (q1 << 8) | (q2 << 16) | (q3 << 24);
+                }
+            if (TABLE) {
+                if (lane == 0) store_header(o, f32_to_f16_bits(scale), f32_to_f16_bits(mn));
+                for (int64_t c = 4 + D + lane; c < out_stride; c += 32) o[c] = 0;
+            } else if (lane == 0) {
+                // D is a multiple of 4 and rows are 4-byte aligned here
+                *reinterpret_cast<uint32_t*>(o + D) = __float_as_uint(scale);
+                *reinterpret_cast<uint32_t*>(o + D + 4) = __float_as_uint(mn);
+            }
+        }
+    }
+}
+
+// 8-bit rows back to fp32, batched the same way: D = 4 * n <= 512, ROWS rows per warp in flight.
+template <int VPL, int ROWS>
+__global__ void __launch_bounds__(kThreads)
+dequantize_8bit_batched_kernel(const uint8_t* __restrict__ in, int64_t N, int64_t Dq, float* __restrict__ out)
+{
+    const int lane = threadIdx.x & 31;
+    const int64_t nwarps = static_cast<int64_t>(gridDim.x) * (kThreads / 32);
+    const int64_t warp = static_cast<int64_t>(blockIdx.x) * (kThreads / 32) + (threadIdx.x >> 5);
+    const int64_t D = Dq - 8;
+    const int nvec = static_cast<int>(D / 4);
+    for (int64_t r0 = warp * ROWS; r0 < N; r0 += nwarps * ROWS) {
+        uint32_t w[ROWS][VPL];
+        uint32_t sb[ROWS][2];
+#pragma unroll
+        for (int j = 0; j < ROWS; ++j) {
+            if (r0 + j >= N) continue;
+            const uint8_t* q = in + (r0 + j) * Dq;
+#pragma unroll
+            for (int v = 0; v < VPL; ++v)
+                if (lane + 32 * v < nvec) w[j][v] = ldg4(q + 4 * (lane + 32 * v));
+            sb[j][0] = ldg4(q + D);
+            sb[j][1] = ldg4(q + D + 4);
+        }
+#pragma unroll
+        for (int j = 0; j < ROWS; ++j) {
+            if (r0 + j >= N) continue;
+            const float scale = __uint_as_float(sb[j][0]), bias = __uint_as_float(sb[j][1]);
+            float4* o = reinterpret_cast<float4*>(out + (r0 + j) * D);
+#pragma unroll
+            for (int v = 0; v < VPL; ++v)
+                if (lane + 32 * v < nvec) {
+                    const uint32_t x = w[j][v];
+                    float4 f;
+                    f.x = fmaf(static_cast<float>(x & 0xffu), scale, bias);
+                    f.y = fmaf(static_cast<float>((x >> 8) & 0xffu), scale, bias);
+                    f.z = fmaf(static_cast<float>((x >> 16) & 0xffu), scale, bias);
+                    f.w = fmaf(static_cast<float>(x >> 24), scale, bias);
+                    o[lane + 32 * v] = f;
+                }
+        }
+    }
+}
+
 template <typename OutT>
 __device__ __forceinline__ void store_deq(OutT* p, float v);
 template <>
@@ -317,6 +420,20 @@ int launch_rows(K kernel, int lpr, int64_t N, cudaStream_t s, const char* name, 
 int quantize_8bit_impl(const void* input, int in_is_half, int64_t N, int64_t D, uint8_t* out, int64_t out_stride,
                        bool table, cudaStream_t s)
 {
+    // fp32 rows of the common widths take the batched kernel
+    if (!in_is_half && D >= 32 && D <= 512 && D % 4 == 0 && (reinterpret_cast<uintptr_t>(input) & 15) == 0 && out_stride % 4 == 0 &&
+        (reinterpret_cast<uintptr_t>(out) & 3) == 0 && N > 0) {
+        const float* x = static_cast<const float*>(input);
+        const int64_t groups = (N + 3) / 4;                                  // at most 4 rows per warp and step
+        const int64_t want = (groups + kThreads / 32 - 1) / (kThreads / 32);
+        const int64_t cap = static_cast<int64_t>(sm_count()) * 8;
+        const unsigned blocks = static_cast<unsigned>(want < cap ? want : cap);
+#define TBE_Q8B(TAB, VPL, ROWS) quantize_8bit_batched_kernel<TAB, VPL, ROWS><<<blocks, kThreads, 0, s>>>(x, N, D, out, out_stride)
+        if (table) { if (D <= 128) TBE_Q8B(true, 1, 4); else if (D <= 256) TBE_Q8B(true, 2, 2); else TBE_Q8B(true, 4, 1); }
+        else { if (D <= 128) TBE_Q8B(false, 1, 4); else if (D <= 256) TBE_Q8B(false, 2, 2); else TBE_Q8B(false, 4, 1); }
+#undef TBE_Q8B
+        return check_launch("quantize_8bit_batched_kernel");
+    }
     const int lpr = (D <= 64) ? 8 : 32;
 #define TBE_Q8(LPR, T, TAB) \
     return launch_rows(quantize_8bit_kernel<LPR, T, TAB>, LPR, N, s, "quantize_8bit_kernel", static_cast<const T*>(input), N, D, out, out_stride)
@@ -365,6 +482,19 @@ extern "C" int tbe_b200_dequantize_8bit_rowwise(const uint8_t* input, int64_t nr
         return fail(TBE_B200_ERR_INVALID_ARGUMENT, "dequantize_8bit_rowwise: rows need at least the 8 scale/bias bytes");
     if (nrows > 0 && (!input || !output)) return fail(TBE_B200_ERR_INVALID_ARGUMENT, "dequantize_8bit_rowwise: NULL pointer");
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+    const int64_t D = ncols_q - 8;
+    if (!out_is_half && D >= 32 && D <= 512 && D % 4 == 0 && (reinterpret_cast<uintptr_t>(input) & 3) == 0 &&
+        (reinterpret_cast<uintptr_t>(output) & 15) == 0 && nrows > 0) {
+        const int64_t groups = (nrows + 3) / 4;
+        const int64_t want = (groups + kThreads / 32 - 1) / (kThreads / 32);
+        const int64_t cap = static_cast<int64_t>(sm_count()) * 8;
+        const unsigned blocks = static_cast<unsigned>(want < cap ? want : cap);
+        float* o = static_cast<float*>(output);
+        if (D <= 128) dequantize_8bit_batched_kernel<1, 4><<<blocks, kThreads, 0, s>>>(input, nrows, ncols_q, o);
+        else if (D <= 256) dequantize_8bit_batched_kernel<2, 2><<<blocks, kThreads, 0, s>>>(input, nrows, ncols_q, o);
+        else dequantize_8bit_batched_kernel<4, 1><<<blocks, kThreads, 0, s>>>(input, nrows, ncols_q, o);
+        return check_launch("dequantize_8bit_batched_kernel");
+    }
     const int lpr = (ncols_q - 8 <= 64) ? 8 : 32;
     if (out_is_half) {
         if (lpr == 8) return launch_rows(dequantize_8bit_kernel<8, __half>, 8, nrows, s, "dequantize_8bit_kernel", input, nrows, ncols_q, static_cast<__half*>(output));
