@@ -350,6 +350,59 @@ dequantize_nbit_kernel(const uint8_t* __restrict__ in, int64_t N, int64_t Dq, fl
     }
 }
 
+// 4-bit rows back to fp32, batched: D a multiple of 8, rows 4-byte aligned.  LPR lanes share a row, a lane turns
+// one 4-byte word (8 codes) into two float4 stores; PASSES passes of 32 / LPR rows are in flight per warp.
+template <int LPR, int VPL, int PASSES>
+__global__ void __launch_bounds__(kThreads)
+dequantize_4bit_batched_kernel(const uint8_t* __restrict__ in, int64_t N, int64_t Dq, float* __restrict__ out)
+{
+    constexpr int RPP = 32 / LPR;          // rows per pass
+    constexpr int RPS = RPP * PASSES;      // rows per warp and step
+    const int lane = threadIdx.x & 31;
+    const int k = lane % LPR, g = lane / LPR;
+    const int64_t nwarps = static_cast<int64_t>(gridDim.x) * (kThreads / 32);
+    const int64_t warp = static_cast<int64_t>(blockIdx.x) * (kThreads / 32) + (threadIdx.x >> 5);
+    const int64_t pbytes = Dq - 4;
+    const int64_t D = pbytes * 2;
+    const int nwords = static_cast<int>(pbytes / 4);
+    for (int64_t r0 = warp * RPS; r0 < N; r0 += nwarps * RPS) {
+        uint32_t w[PASSES][VPL], hdr[PASSES];
+#pragma unroll
+        for (int j = 0; j < PASSES; ++j) {
+            const int64_t r = r0 + j * RPP + g;
+            if (r >= N) continue;
+            const uint8_t* q = in + r * Dq;
+#pragma unroll
+            for (int v = 0; v < VPL; ++v)
+                if (k + LPR * v < nwords) w[j][v] = ldg4(q + 4 * (k + LPR * v));
+            hdr[j] = ldg4(q + pbytes);
+        }
+#pragma unroll
+        for (int j = 0; j < PASSES; ++j) {
+            const int64_t r = r0 + j * RPP + g;
+            if (r >= N) continue;
+            const float scale = half_bits_to_float(hdr[j] & 0xffffu), bias = half_bits_to_float(hdr[j] >> 16);
+            float4* o = reinterpret_cast<float4*>(out + r * D);
+#pragma unroll
+            for (int v = 0; v < VPL; ++v)
+                if (k + LPR * v < nwords) {
+                    const uint32_t x = w[j][v];
+                    float4 a, b;
+                    a.x = fmaf(static_cast<float>(x & 15u), scale, bias);
+                    a.y = fmaf(static_cast<float>((x >> 4) & 15u), scale, bias);
+                    a.z = fmaf(static_cast<float>((x >> 8) & 15u), scale, bias);
+                    a.w = fmaf(static_cast<float>((x >> 12) & 15u), scale, bias);
+                    b.x = fmaf(static_cast<float>((x >> 16) & 15u), scale, bias);
+                    b.y = fmaf(static_cast<float>((x >> 20) & 15u), scale, bias);
+                    b.z = fmaf(static_cast<float>((x >> 24) & 15u), scale, bias);
+                    b.w = fmaf(static_cast<float>(x >> 28), scale, bias);
+                    o[2 * (k + LPR * v)] = a;
+                    o[2 * (k + LPR * v) + 1] = b;
+                }
+        }
+    }
+}
+
 // ---- packing quantizer output into table rows ----------------------------------
 
 template <int SRC_BITS>
@@ -525,6 +578,17 @@ extern "C" int tbe_b200_dequantize_nbit_rowwise_sbhalf(int32_t bit_rate, const u
         return fail(TBE_B200_ERR_INVALID_ARGUMENT, "dequantize_nbit_rowwise_sbhalf: rows need at least the 4 scale/bias bytes");
     if (nrows > 0 && (!input || !output)) return fail(TBE_B200_ERR_INVALID_ARGUMENT, "dequantize_nbit_rowwise_sbhalf: NULL pointer");
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+    const int64_t pb = ncols_q - 4;
+    if (bit_rate == 4 && pb >= 16 && pb % 4 == 0 && pb <= 512 && (reinterpret_cast<uintptr_t>(input) & 3) == 0 &&
+        (reinterpret_cast<uintptr_t>(output) & 15) == 0 && nrows > 0) {
+        const int64_t want = (nrows + 8 * (kThreads / 32) - 1) / (8 * (kThreads / 32));
+        const int64_t cap = static_cast<int64_t>(sm_count()) * 8;
+        const unsigned blocks = static_cast<unsigned>(want < cap ? want : cap);
+        if (pb <= 64) dequantize_4bit_batched_kernel<16, 1, 4><<<blocks, kThreads, 0, s>>>(input, nrows, ncols_q, output);
+        else if (pb <= 128) dequantize_4bit_batched_kernel<32, 1, 4><<<blocks, kThreads, 0, s>>>(input, nrows, ncols_q, output);
+        else dequantize_4bit_batched_kernel<32, 4, 2><<<blocks, kThreads, 0, s>>>(input, nrows, ncols_q, output);
+        return check_launch("dequantize_4bit_batched_kernel");
+    }
     if (bit_rate == 4) return launch_rows(dequantize_nbit_kernel<4>, 32, nrows, s, "dequantize_nbit_kernel", input, nrows, ncols_q, output);
     return launch_rows(dequantize_nbit_kernel<2>, 32, nrows, s, "dequantize_nbit_kernel", input, nrows, ncols_q, output);
 }

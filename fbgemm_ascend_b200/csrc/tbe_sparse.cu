@@ -178,32 +178,37 @@ __global__ void __launch_bounds__(256) permute_lengths_kernel(const T* __restric
 // Output position o lies in output table i with out_off[i] <= o < out_off[i + 1]; its source is
 // in_off[permute[i]] + (o - out_off[i]).  A thread finds the table of its first position by binary search
 // and walks forward from there.  VT is the unit copied per position (the element, or 16 bytes of a wide row).
-template <typename VT>
+template <typename VT, bool ONE_UNIT>
 __global__ void __launch_bounds__(256) permute_segments_kernel(const VT* __restrict__ src, VT* __restrict__ dst, int64_t units_per_pos,
                                                                int64_t capacity /* positions */, const int32_t* __restrict__ permute,
                                                                int64_t T_in, int64_t T_out, const int64_t* __restrict__ in_off,
                                                                const int64_t* __restrict__ out_off)
 {
     const int64_t total = min(capacity, out_off[T_out]) * units_per_pos;
-    const int64_t step = static_cast<int64_t>(gridDim.x) * blockDim.x;
-    int64_t i = -1;        // current output table
-    int64_t seg_lo = 0, seg_hi = 0, delta = 0;
-    for (int64_t u = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; u < total; u += step) {
-        const int64_t o = u / units_per_pos;
-        if (i < 0 || o >= seg_hi) {
-            // largest i with out_off[i] <= o
-            int64_t lo = (i < 0) ? 0 : i, hi = T_out;
-            while (hi - lo > 1) {
-                const int64_t mid = (lo + hi) >> 1;
-                if (out_off[mid] <= o) lo = mid; else hi = mid;
+    constexpr int kPerThread = 8;
+    const int64_t chunk = 256 * kPerThread;   // consecutive units of one block and step: a table changes rarely inside
+    int64_t i = -1;                            // current output table
+    int64_t seg_hi = 0, delta = 0;
+    for (int64_t c0 = static_cast<int64_t>(blockIdx.x) * chunk; c0 < total; c0 += static_cast<int64_t>(gridDim.x) * chunk) {
+#pragma unroll 4
+        for (int j = 0; j < kPerThread; ++j) {
+            const int64_t u = c0 + j * 256 + threadIdx.x;
+            if (u >= total) break;
+            const int64_t o = ONE_UNIT ? u : u / units_per_pos;   // a position is one unit for plain values
+            if (i < 0 || o >= seg_hi) {
+                // largest i with out_off[i] <= o; positions only grow, so the search starts at the current table
+                int64_t lo = (i < 0) ? 0 : i, hi = T_out;
+                while (hi - lo > 1) {
+                    const int64_t mid = (lo + hi) >> 1;
+                    if (out_off[mid] <= o) lo = mid; else hi = mid;
+                }
+                i = lo;
+                seg_hi = out_off[i + 1];
+                const int64_t p = permute[i];
+                delta = ((p >= 0 && p < T_in) ? in_off[p] : 0) - out_off[i];
             }
-            i = lo;
-            seg_lo = out_off[i];
-            seg_hi = out_off[i + 1];
-            const int64_t p = permute[i];
-            delta = ((p >= 0 && p < T_in) ? in_off[p] : 0) - seg_lo;
+            dst[u] = src[u + (ONE_UNIT ? delta : delta * units_per_pos)];
         }
-        dst[u] = src[u + delta * units_per_pos];
     }
 }
 
@@ -213,11 +218,15 @@ int launch_segments(const void* src, void* dst, int64_t units_per_pos, int64_t c
 {
     const int64_t units = capacity * units_per_pos;
     if (units <= 0) return TBE_B200_OK;
-    const int64_t want = (units + 256 * 4 - 1) / (256 * 4);   // about four units per thread
+    const int64_t want = (units + 256 * 8 - 1) / (256 * 8);   // eight units per thread and step
     const int64_t cap = static_cast<int64_t>(sm_count()) * 32;
     const unsigned blocks = static_cast<unsigned>(want < cap ? want : cap);
-    permute_segments_kernel<VT><<<blocks, 256, 0, s>>>(static_cast<const VT*>(src), static_cast<VT*>(dst), units_per_pos, capacity, permute,
-                                                       T_in, T_out, in_off, out_off);
+    if (units_per_pos == 1)
+        permute_segments_kernel<VT, true><<<blocks, 256, 0, s>>>(static_cast<const VT*>(src), static_cast<VT*>(dst), 1, capacity, permute, T_in,
+                                                                 T_out, in_off, out_off);
+    else
+        permute_segments_kernel<VT, false><<<blocks, 256, 0, s>>>(static_cast<const VT*>(src), static_cast<VT*>(dst), units_per_pos, capacity,
+                                                                  permute, T_in, T_out, in_off, out_off);
     return check_launch("permute_segments_kernel");
 }
 
