@@ -5,24 +5,18 @@
 // int_nbit_split_embedding_nobag_kernel.h:31-398).  The path is a gather and a
 // reduction bounded by HBM/L2 bandwidth, so there is no tensor-core work here.
 //
-// Pooled kernel, one warp per bag (t, b):
-//   * the warp reads up to 32 of the bag's indices (and per-sample weights) with one
-//     coalesced load and hands them out with shuffles;
-//   * LPR lanes (2..32, a power of two chosen from the row width) cooperate on one
-//     row, so 32/LPR rows of the bag are fetched concurrently, each lane with one
-//     16-byte (INT8/FP8/FP16/FP32) or 8-byte (INT4) load; rows are dequantised in
-//     registers with the row's fp16 scale/bias and accumulated in fp32, 16
-//     accumulators per lane;
-//   * INT8/INT4 rows start with a 4-byte header, which shifts the payload off the
-//     16-byte grid.  The lane that loads the header chunk has 4 (INT8) or 8 (INT4)
-//     free slots; when D is a multiple of 16 they take the row's last elements,
-//     which would otherwise need one more lane.  D = 16*LPR rows then keep every
-//     lane busy with exactly 16 elements;
-//   * the per-group partial sums are combined with a reduce-scatter over
-//     shuffles, after which every lane owns 16*LPR/32 finished elements and
-//     stores them (8- or 16-byte stores);
-//   * rows of any other shape (row_alignment 1, odd D, INT2, unaligned tables)
-//     take a byte-wise path with the same results.
+// Pooled kernel (SUM / MEAN), in three tiers chosen per table:
+//   * aligned rows of INT8 / INT4 / FP8 / FP16 / FP32 with D a multiple of 16 up to 512 (pool_run_staged): LPR lanes
+//     share a row, 16 fp32 accumulators per lane, so a warp has 32/LPR lane groups; the groups pool that many
+//     consecutive bags side by side (or split one long bag and reduce-scatter at the end).  Rows reach shared
+//     memory by one bulk asynchronous copy each (cp.async.bulk, completion on an mbarrier), up to 32 per warp in
+//     flight; they are dequantised with the row's fp16 scale/bias (codes -> exact fp16 by a magic constant, then
+//     fp16 x fp16 + fp32 mixed FMA) and accumulated in fp32.  INT8/INT4 rows start with a 4-byte header, which
+//     shifts the payload off the 16-byte grid; the lane that reads the header chunk has 4 / 8 free slots, which
+//     take the row's last elements, so D = 16*LPR rows keep every lane busy with exactly 16 elements;
+//   * other aligned shapes (pool_bag): one warp per bag, cp.async staging in chunks, cross-group reduce-scatter;
+//   * anything else (row_alignment 1, odd D, INT2 or BF16 rows, unaligned tables): a byte-wise path.
+// Sequence mode (pooling NONE): tbe_nobag_kernel, 64 consecutive positions per warp.
 #include <stdarg.h>
 #include <stdio.h>
 #include <stdlib.h>
@@ -1258,7 +1252,7 @@ __device__ __forceinline__ bool pool_run_staged_by_type(const LookupParams& p, c
 // ---- kernels -----------------------------------------------------------------
 
 constexpr int kWarpsPerBlock = 4;
-constexpr int kMinBlocksPerSM = 8;   // 32 resident warps per SM: 64 registers and 5 KB of staging memory per warp
+constexpr int kMinBlocksPerSM = 8;   // 32 resident warps per SM: 64 registers and 6 KB of staging memory per warp
 
 // The T*B bags (bag i = t*B + b) are cut into spans of `span` consecutive bags, one span per warp, so a
 // warp walks `offsets`, `indices` and the per-sample weights front to back.  A span is processed as runs
