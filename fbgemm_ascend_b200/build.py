@@ -2,8 +2,6 @@
 
 ``lib/libtbe_b200.so``      CUDA kernels + the C ABI of ``include/tbe_b200.h``; no torch in it.
 ``lib/libtbe_b200_torch.so``  the ``torch.ops.fbgemm.*`` registrations, calling the C ABI.
-``lib/tbe_b200_row_gather_probe``  stand-alone measurement program: the row-gather ceiling of the device
-                            (``bench.py --probe-gather`` runs it); not linked into the libraries.
 
 One architecture, one ``nvcc`` invocation per source file: this replaces the
 reference's chip detection and per-SoC operator packages
@@ -29,9 +27,8 @@ INCLUDE = os.path.join(ROOT, "include")
 
 CABI_LIB = os.path.join(LIB_DIR, "libtbe_b200.so")
 TORCH_LIB = os.path.join(LIB_DIR, "libtbe_b200_torch.so")
-PROBE_BIN = os.path.join(LIB_DIR, "tbe_b200_row_gather_probe")
 
-CUDA_SOURCES = ["tbe_common.cu", "tbe_lookup.cu", "tbe_quant.cu", "tbe_permute.cu", "tbe_sparse.cu"]
+CUDA_SOURCES = ["tbe_common.cu", "tbe_lookup.cu", "tbe_quant.cu", "tbe_permute.cu", "tbe_sparse.cu", "tbe_exchange.cu"]
 NVCC_FLAGS = ["-O3", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
               "-Xcompiler", "-fPIC", "-I" + INCLUDE]
 
@@ -97,20 +94,11 @@ def build_torch(force: bool = False, verbose: bool = False) -> str:
     return TORCH_LIB
 
 
-def build_probe(force: bool = False, verbose: bool = False) -> str:
-    src = os.path.join(CSRC, "row_gather_probe.cu")
-    if force or _newer(PROBE_BIN, [src]):
-        os.makedirs(LIB_DIR, exist_ok=True)
-        _run([_nvcc(), "-O3", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", src, "-o", PROBE_BIN], verbose)
-    return PROBE_BIN
-
-
 def build(force: bool = False, verbose: bool = False) -> None:
     build_cabi(force, verbose)
     build_torch(force, verbose)
-    build_probe(force, verbose)
 
 
 if __name__ == "__main__":
     build(force="--force" in sys.argv, verbose=True)
-    print("built", CABI_LIB, TORCH_LIB, PROBE_BIN)
+    print("built", CABI_LIB, TORCH_LIB)

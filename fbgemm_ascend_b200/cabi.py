@@ -46,6 +46,8 @@ EXPORTS = {
     "tbe_b200_permute_2d_sparse_scratch_bytes": (_i64, [_i64, _i64]),
     "tbe_b200_permute_2d_sparse_offsets": (_i32, [_vp, _i64, _vp, _i32, _i64, _i64, _vp, _vp, _i64, _vp, _vp]),
     "tbe_b200_permute_2d_sparse_copy": (_i32, [_vp, _i64, _i64, _vp, _i64, _vp, _i64, _vp, _vp, _i64, _vp, _vp]),
+    "tbe_b200_signal_peers": (_i32, [_vp, _i32, _i32, _i64, _vp]),
+    "tbe_b200_wait_flags": (_i32, [_vp, _i32, _i64, _i64, _vp, _vp]),
     "tbe_b200_last_error": (C.c_char_p, []),
     "tbe_b200_version": (_i32, []),
 }
@@ -166,3 +168,15 @@ def permute_pooled_embs_blocked(blocks: torch.Tensor, offset_dim_list: torch.Ten
                                                      _ptr(inv_offset_dim_list), permute_list.numel(), _ptr(output),
                                                      _ptr(error_flag), _stream()), "tbe_b200_permute_pooled_embs_blocked")
     return output
+
+
+def signal_peers(peer_flag_ptrs: torch.Tensor, world: int, rank: int, value: int) -> None:
+    """``tbe_b200_signal_peers`` on the current stream; ``peer_flag_ptrs`` is an int64 CUDA tensor of ``world``
+    addresses, one per rank, each of an int64 flag array of ``world`` entries in that rank's memory."""
+    check(lib().tbe_b200_signal_peers(_ptr(peer_flag_ptrs), world, rank, value, _stream()), "tbe_b200_signal_peers")
+
+
+def wait_flags(flags: torch.Tensor, world: int, value: int, max_polls: int, error_flag: Optional[torch.Tensor] = None) -> None:
+    """``tbe_b200_wait_flags`` on the current stream: a bounded device-side wait for ``flags[r] >= value``."""
+    assert flags.dtype == torch.int64 and flags.numel() >= world
+    check(lib().tbe_b200_wait_flags(_ptr(flags), world, value, max_polls, _ptr(error_flag), _stream()), "tbe_b200_wait_flags")

@@ -2,6 +2,8 @@
 #include <stdarg.h>
 #include <stdio.h>
 
+#include <atomic>
+
 #include "tbe_common.cuh"
 
 namespace tbe {
@@ -29,15 +31,15 @@ int check_launch(const char* what)
 int sm_count()
 {
     constexpr int kMaxDev = 64;
-    static int cached[kMaxDev] = {0};
+    static std::atomic<int> cached[kMaxDev];   // zero-initialised; a lost race only repeats the query
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDev) return 148;
-    if (cached[dev] == 0) {
-        int n = 0;
+    int n = cached[dev].load(std::memory_order_relaxed);
+    if (n == 0) {
         if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
-        cached[dev] = n;
+        cached[dev].store(n, std::memory_order_relaxed);
     }
-    return cached[dev];
+    return n;
 }
 
 }  // namespace tbe

@@ -6,20 +6,24 @@
 // reduction bounded by HBM/L2 bandwidth, so there is no tensor-core work here.
 //
 // Pooled kernel (SUM / MEAN), in three tiers chosen per table:
-//   * aligned rows of INT8 / INT4 / FP8 / FP16 / FP32 with D a multiple of 16 up to 512 (pool_run_staged): LPR lanes
-//     share a row, 16 fp32 accumulators per lane, so a warp has 32/LPR lane groups; the groups pool that many
-//     consecutive bags side by side (or split one long bag and reduce-scatter at the end).  Rows reach shared
-//     memory by one bulk asynchronous copy each (cp.async.bulk, completion on an mbarrier), up to 32 per warp in
-//     flight; they are dequantised with the row's fp16 scale/bias (codes -> exact fp16 by a magic constant, then
-//     fp16 x fp16 + fp32 mixed FMA) and accumulated in fp32.  INT8/INT4 rows start with a 4-byte header, which
-//     shifts the payload off the 16-byte grid; the lane that reads the header chunk has 4 / 8 free slots, which
-//     take the row's last elements, so D = 16*LPR rows keep every lane busy with exactly 16 elements;
-//   * other aligned shapes (pool_bag): one warp per bag, cp.async staging in chunks, cross-group reduce-scatter;
+//   * aligned rows of INT8 / INT4 / FP8 / FP16 / FP32 with D a multiple of 16 up to 512 (pool_run_stream): LPR lanes
+//     share a row, 16 fp32 accumulators per lane, so a warp has 32/LPR lane groups.  The rows of a warp's bags are
+//     cut into equal ranges, one per group, and every group streams its range through a small ring in shared
+//     memory: asynchronous 16-byte copies through L1 (which holds the hot head of a Zipf-distributed table), several
+//     rows per group in flight, consumed in order; bags that straddle two ranges are combined through shared memory.  Rows are dequantised
+//     with the row's fp16 scale/bias (codes -> exact fp16 by a magic constant, then fp16 x fp16 + fp32 mixed FMA)
+//     and accumulated in fp32.  INT8/INT4 rows start with a 4-byte header, which shifts the payload off the
+//     16-byte grid; the lane that reads the header chunk has 4 / 8 free slots, which take the row's last
+//     elements, so D = 16*LPR rows keep every lane busy with exactly 16 elements;
+//   * other aligned shapes (pool_bag; only in the build of the kernel for wide tables): one warp per bag, cp.async
+//     staging in chunks, cross-group reduce-scatter;
 //   * anything else (row_alignment 1, odd D, INT2 or BF16 rows, unaligned tables): a byte-wise path.
 // Sequence mode (pooling NONE): tbe_nobag_kernel, 64 consecutive positions per warp.
 #include <stdarg.h>
 #include <stdio.h>
 #include <stdlib.h>
+
+#include <atomic>
 
 #include "tbe_common.cuh"
 
@@ -54,6 +58,8 @@ struct LookupParams {
     int32_t row_alignment;
     uint32_t fp8_shift;  // 16 + exponent bits
     float fp8_mult;      // 2^(127 - bias)
+    int64_t dev_weights_bytes;   // size of dev_weights, 0 = unknown
+    int32_t idx64;       // indices and offsets are 64-bit
 };
 
 __host__ __device__ inline int64_t row_bytes_of(int ty, int D, int align)
@@ -127,6 +133,24 @@ __device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, int bytes)
 {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
+}
+// The same through L1 (the line stays cached for the rows that are fetched again and again).
+__device__ __forceinline__ void cp_async16_ca(uint32_t dst, const void* src, int bytes)
+{
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
+}
+// Experiment (TBE_L2_HINTS builds only): the row copies carry an L2 evict-last policy.  Measured slower than the plain
+// form: the policy operand travels through the uniform datapath and costs extra instructions per copy in a kernel
+// that is bound by instruction issue, and the L2 hit rate does not move (the hot rows stay in L2 anyway).
+__device__ __forceinline__ uint64_t l2_policy_evict_last()
+{
+    uint64_t pol;
+    asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(pol));
+    return pol;
+}
+__device__ __forceinline__ void cp_async16_ca_hint(uint32_t dst, const void* src, int bytes, uint64_t pol)
+{
+    asm volatile("cp.async.ca.shared.global.L2::cache_hint [%0], [%1], 16, %2, %3;" ::"r"(dst), "l"(src), "r"(bytes), "l"(pol) : "memory");
 }
 __device__ __forceinline__ void cp_async8(uint32_t dst, const void* src, int bytes)
 {
@@ -471,6 +495,7 @@ struct BagInfo {
     void* seg;              // output address of element 0 of the bag
     float mean_mul;         // 1/L for MEAN, else 1
     bool seg_aligned;       // seg is 16-byte aligned
+    int64_t avail;          // bytes of the table: a row that would end past them is skipped
 };
 
 // Up to 32 consecutive indices and weights of a bag, one per lane.  Indices are narrowed to 32 bits:
@@ -481,16 +506,18 @@ struct BagHead {
 };
 
 template <typename IdxT>
-__device__ __forceinline__ BagHead load_batch(const IdxT* indices, const float* pw, int n, int lane, int32_t* error_flag)
+__device__ __forceinline__ BagHead load_batch(const IdxT* indices, const float* pw, int n, int lane, int32_t* error_flag,
+                                              int64_t stride, int64_t avail)
 {
     BagHead h;
     h.idx = -1;
     h.w = 1.0f;
     if (lane < n) {
-        const IdxT v = __ldg(indices + lane);
-        const bool bad = (v < static_cast<IdxT>(-1)) || (sizeof(IdxT) == 8 && static_cast<int64_t>(v) > 0x7fffffffll);
-        h.idx = bad ? -1 : static_cast<int32_t>(v);
-        if (bad && error_flag) atomicOr(error_flag, 1);
+        const int64_t v = static_cast<int64_t>(__ldg(indices + lane));
+        const bool bad = (v < -1) || (v > 0x7fffffffll);
+        const bool past = !bad && v >= 0 && static_cast<uint64_t>(v + 1) * static_cast<uint64_t>(stride) > static_cast<uint64_t>(avail);
+        h.idx = (bad || past) ? -1 : static_cast<int32_t>(v);
+        if ((bad || past) && error_flag) atomicOr(error_flag, bad ? 1 : 4);
         if (pw) h.w = __ldg(pw + lane);
     }
     return h;
@@ -547,7 +574,7 @@ __device__ __forceinline__ void pool_bag(const LookupParams& p, const BagInfo& b
             if (row0 >= batch0 + kWarp) {
                 batch0 += kWarp;
                 const BagHead nb = load_batch<IdxT>(indices + batch0, pw ? pw + batch0 : nullptr, bag.L - batch0, lane,
-                                                    cx.first_blk ? p.error_flag : nullptr);
+                                                    cx.first_blk ? p.error_flag : nullptr, bag.stride, bag.avail);
                 my_idx = nb.idx;
                 my_w = nb.w;
             }
@@ -635,6 +662,7 @@ struct TableMeta {
     const uint8_t* table;   // first row
     int64_t stride;         // bytes per row
     int64_t col;            // output column of the table
+    int64_t avail;          // bytes of dev_weights the table's rows may occupy (a row past them is not read)
     int32_t ty;
     int32_t D;
     bool rows_aligned;      // table start and row stride are multiples of 16 bytes
@@ -650,6 +678,17 @@ __device__ __forceinline__ TableMeta load_meta(const LookupParams& p, int t)
     m.col = p.out_cols ? p.out_cols[t] : static_cast<int64_t>(d0);
     m.stride = row_bytes_of(m.ty, m.D, p.row_alignment);
     m.rows_aligned = ((reinterpret_cast<uintptr_t>(m.table) | static_cast<uint64_t>(m.stride)) & 15) == 0;
+    // The table ends where the next one starts (tables laid out in order) or, failing that, where dev_weights ends.
+    m.avail = 0x7fffffffffffffffll;
+    if (p.dev_weights_bytes > 0) {
+        const int64_t start = p.weights_offsets[t];
+        int64_t end = p.dev_weights_bytes;
+        if (t + 1 < p.T) {
+            const int64_t next = p.weights_offsets[t + 1];
+            if (next > start && next < end) end = next;
+        }
+        m.avail = end > start ? end - start : 0;
+    }
     return m;
 }
 
@@ -701,7 +740,7 @@ template <typename IdxT>
 __device__ __noinline__ void pool_bag_bytewise(const IdxT* indices, const float* pw, int32_t* error_flag,
                                                const uint8_t* table, int64_t stride, int L, int D, void* seg,
                                                float mean_mul, int ty, int out_ty, uint32_t fp8_shift,
-                                               float fp8_mult, int lane)
+                                               float fp8_mult, int lane, int64_t avail)
 {
     for (int e_blk = 0; e_blk < D; e_blk += kByteAcc * kWarp) {
         float acc[kByteAcc];
@@ -710,7 +749,11 @@ __device__ __noinline__ void pool_bag_bytewise(const IdxT* indices, const float*
         for (int n = 0; n < L; ++n) {
             const int64_t idx = static_cast<int64_t>(indices[n]);
             if (idx < 0) {
-                if (idx < -1 && lane == 0 && error_flag) atomicOr(error_flag, 1);
+                if (idx < -1 && lane == 0 && error_flag && e_blk == 0) atomicOr(error_flag, 1);
+                continue;
+            }
+            if (idx > 0x7fffffffll || static_cast<uint64_t>(idx + 1) * static_cast<uint64_t>(stride) > static_cast<uint64_t>(avail)) {
+                if (lane == 0 && error_flag && e_blk == 0) atomicOr(error_flag, idx > 0x7fffffffll ? 1 : 4);
                 continue;
             }
             const float w = pw ? pw[n] : 1.0f;
@@ -731,61 +774,42 @@ __device__ __noinline__ void pool_bag_bytewise(const IdxT* indices, const float*
     }
 }
 
-// ---- the common shapes: rows staged in shared memory by bulk copies, groups of lanes --------
-//
-// One bulk asynchronous copy (cp.async.bulk, executed by the copy engine of the SM) moves a whole row
-// from global to shared memory; its completion is counted on an mbarrier.  Every lane of a warp issues
-// the copy of a different row, so up to 32 rows per warp are in flight with one instruction and no
-// register holds data that is still on its way.  Source, destination and size are multiples of 16
-// bytes by construction (aligned tables, padded row stride).
+// ---- the common shapes: rows streamed through a shared-memory ring, groups of lanes -----------------
 
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count)
-{
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar)
-{
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive_expect(uint32_t bar, uint32_t bytes)
-{
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void bulk_copy_row(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar)
-{
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(src),
-                 "r"(bytes), "r"(bar)
-                 : "memory");
-}
-// Orders this thread's earlier shared-memory accesses before its later asynchronous copies.
-__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+// Zeros that stand in for a row that must not be added: zero payload, and for INT8 / INT4 a zero header (scale 0, bias 0).
+__device__ __align__(16) const uint8_t g_zero_row[2048] = {0};
 
-// Waits for the phase with the given parity.  The wait is bounded: false after kWaitTries polls.
-constexpr int kWaitTries = 1 << 22;
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity)
+// Read-once streams (indices, per-sample weights): not kept in L1.
+__device__ __forceinline__ int64_t ld_once64(const void* p) { return ld_stream(static_cast<const int64_t*>(p)); }
+__device__ __forceinline__ int32_t ld_once32(const void* p) { return ld_stream(static_cast<const int32_t*>(p)); }
+__device__ __forceinline__ float ld_once_f32(const void* p) { return ld_stream(static_cast<const float*>(p)); }
+
+__device__ __forceinline__ void sts16(uint32_t a, float x, float y, float z, float w)
 {
-    for (int t = 0; t < kWaitTries; ++t) {
-        uint32_t done;
-        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-                     : "=r"(done)
-                     : "r"(bar), "r"(parity)
-                     : "memory");
-        if (done) return true;
-    }
-    return false;
+    asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(a), "f"(x), "f"(y), "f"(z), "f"(w) : "memory");
+}
+__device__ __forceinline__ void sts4(uint32_t a, int32_t v) { asm volatile("st.shared.b32 [%0], %1;" ::"r"(a), "r"(v) : "memory"); }
+__device__ __forceinline__ float4 lds16f(uint32_t a)
+{
+    float4 v;
+    asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(a) : "memory");
+    return v;
+}
+__device__ __forceinline__ int32_t lds4i(uint32_t a)
+{
+    int32_t v;
+    asm volatile("ld.shared.b32 %0, [%1];" : "=r"(v) : "r"(a) : "memory");
+    return v;
 }
 
-// Adds one INT8 / INT4 row chunk to a lane's 16 slots.  `w0` is the lane's first payload word (the row's tail
-// on the header lane), words[1..] the rest of its chunk, `hdr` the row header (fp16 scale, fp16 bias; zero
-// for a row that is not to be added).
-template <int TY, bool WEIGHTED, bool FOLD>
-__device__ __forceinline__ void accum_header_row(uint32_t w0, const uint32_t (&words)[4], uint32_t hdr, float w, float (&acc)[16],
-                                                 float& bias_acc, float& scale_acc)
+// The header of an INT8 / INT4 row (fp16 scale, fp16 bias; zero for a row that is not to be added): adds the bias
+// (and, in the folded form, the scale) to the bag's running sums and returns the scale's fp16 bits; `ws` is
+// scale * w for the weighted form.
+template <bool WEIGHTED, bool FOLD>
+__device__ __forceinline__ unsigned short accum_header(uint32_t hdr, float w, float& ws, float& bias_acc, float& scale_acc)
 {
-    constexpr bool k8 = (TY == TBE_B200_INT8);
     const unsigned short scale_h = static_cast<unsigned short>(hdr & 0xffffu);
-    float ws = 0.0f;
+    ws = 0.0f;
     if constexpr (WEIGHTED) {
         ws = half_bits_to_float(scale_h) * w;
         bias_acc = fmaf(half_bits_to_float(hdr >> 16), w, bias_acc);
@@ -793,34 +817,53 @@ __device__ __forceinline__ void accum_header_row(uint32_t w0, const uint32_t (&w
         bias_acc += half_bits_to_float(hdr >> 16);
         if constexpr (FOLD) scale_acc += half_bits_to_float(scale_h);
     }
-    if (k8) {
+    return scale_h;
+}
+
+// Adds NW 32-bit words of INT8 (4 per word) or INT4 (8 per word) codes, times the row scale, to consecutive slots
+// of `acc` (a compile-time position inside the lane's accumulators).
+template <int TY, bool WEIGHTED, bool FOLD, int NW>
+__device__ __forceinline__ void accum_codes(const uint32_t (&words)[NW], unsigned short scale_h, float ws, float* acc)
+{
+    if constexpr (TY == TBE_B200_INT8) {
 #pragma unroll
-        for (int i4 = 0; i4 < 4; ++i4) {
-            const uint32_t c = (i4 == 0) ? w0 : words[i4];
+        for (int i = 0; i < NW; ++i) {
+            const uint32_t c = words[i];
             // bytes 0 and 2, then bytes 1 and 3, placed in the mantissas of half2(1024, 1024)
+#ifdef TBE_SPLAT_DECODE
+            if constexpr (FOLD) {
+                // one code per register: bytes (q, 0x64, 0, 0) = the half 1024 + q in the low 16 bits
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const uint32_t x = __byte_perm(c, 0x6400u, 0x4450u | j);
+                    asm("fma.rn.f32.f16 %0, %1, %2, %0;" : "+f"(acc[4 * i + j]) : "h"(static_cast<unsigned short>(x)), "h"(scale_h));
+                }
+                continue;
+            }
+#endif
             uint32_t even = (c & 0x00FF00FFu) | 0x64006400u;
             uint32_t odd = __byte_perm(c, 0x64646464u, 0x4341);
             if constexpr (!FOLD) {
                 even = codes_to_half2(even, 0x64006400u);
                 odd = codes_to_half2(odd, 0x64006400u);
             }
-            add_pair_t<WEIGHTED>(acc[4 * i4 + 0], acc[4 * i4 + 2], even, scale_h, ws);
-            add_pair_t<WEIGHTED>(acc[4 * i4 + 1], acc[4 * i4 + 3], odd, scale_h, ws);
+            add_pair_t<WEIGHTED>(acc[4 * i + 0], acc[4 * i + 2], even, scale_h, ws);
+            add_pair_t<WEIGHTED>(acc[4 * i + 1], acc[4 * i + 3], odd, scale_h, ws);
         }
     } else {
 #pragma unroll
-        for (int i2 = 0; i2 < 2; ++i2) {
-            const uint32_t c = (i2 == 0) ? w0 : words[i2];
+        for (int i = 0; i < NW; ++i) {
+            const uint32_t c = words[i];
             const uint32_t y = c >> 8;
             // nibble pairs (j, j + 4) sit 16 bits apart: 0x6400 | n = 1024 + n; 0x5400 | (n << 4) = 64 + n
             const uint32_t p0 = codes_to_half2((c & 0x000F000Fu) | 0x64006400u, 0x64006400u);   // nibbles 0, 4
             const uint32_t p1 = codes_to_half2((c & 0x00F000F0u) | 0x54005400u, 0x54005400u);   // nibbles 1, 5
             const uint32_t p2 = codes_to_half2((y & 0x000F000Fu) | 0x64006400u, 0x64006400u);   // nibbles 2, 6
             const uint32_t p3 = codes_to_half2((y & 0x00F000F0u) | 0x54005400u, 0x54005400u);   // nibbles 3, 7
-            add_pair_t<WEIGHTED>(acc[8 * i2 + 0], acc[8 * i2 + 4], p0, scale_h, ws);
-            add_pair_t<WEIGHTED>(acc[8 * i2 + 1], acc[8 * i2 + 5], p1, scale_h, ws);
-            add_pair_t<WEIGHTED>(acc[8 * i2 + 2], acc[8 * i2 + 6], p2, scale_h, ws);
-            add_pair_t<WEIGHTED>(acc[8 * i2 + 3], acc[8 * i2 + 7], p3, scale_h, ws);
+            add_pair_t<WEIGHTED>(acc[8 * i + 0], acc[8 * i + 4], p0, scale_h, ws);
+            add_pair_t<WEIGHTED>(acc[8 * i + 1], acc[8 * i + 5], p1, scale_h, ws);
+            add_pair_t<WEIGHTED>(acc[8 * i + 2], acc[8 * i + 6], p2, scale_h, ws);
+            add_pair_t<WEIGHTED>(acc[8 * i + 3], acc[8 * i + 7], p3, scale_h, ws);
         }
     }
 }
@@ -841,334 +884,469 @@ __device__ __forceinline__ char* dest_segment(const LookupParams& p, int64_t b, 
     return static_cast<char*>(p.dests[which]) + (rem * p.out_stride + col) * esz;
 }
 
-constexpr int kStageBytes = kWarpSmemBytes;   // row slots of one warp
+// Shared memory of one warp in the streaming kernel: the partial sums that lane groups hand to one another
+// (up to 32 floats per lane), the run's bag offsets, and the ring of rows in flight.
+constexpr int kPartBytes = kWarp * 128;
+constexpr int kMaxRunBags = 31;                        // bags of one run: their nb + 1 offsets are held one per lane
+constexpr int kRelBytes = 144;                         // (kMaxRunBags + 1) offsets, rounded to 16 bytes
+#ifndef TBE_RING_BYTES
+#define TBE_RING_BYTES 4352                            // four stages of rows with up to 32 bytes per lane
+#endif
+#ifndef TBE_MAX_STAGES
+#define TBE_MAX_STAGES 4
+#endif
+constexpr int kRingBytes = TBE_RING_BYTES;
+constexpr int kStreamSmemBytes = kPartBytes + kRelBytes + kRingBytes;
 
-// A run of consecutive bags of ONE table whose rows are D = 16 * n <= 512 elements, 16-byte aligned.
-// LPR lanes share a row, 16 elements per lane, so a warp has G = 32 / LPR lane groups, and every group
-// walks its OWN range of the index array:
-//   * normally the groups pool G consecutive bags side by side.  Nothing is exchanged between lanes when
-//     a bag is finished -- a lane simply stores its 16 elements -- and all the per-bag work (offsets,
-//     lengths, addresses, conversion, stores) is done for G bags by one instruction stream;
-//   * when the G bags differ too much in length (or fewer than G are left), the warp takes a single bag
-//     and splits its rows over the groups instead; the groups' partial sums are then combined with a
-//     reduce-scatter over shuffles.  Both forms share the row loop.
-// The row loop works in rounds of R rows per group (R * G <= 32 rows, as many as the warp's staging
-// memory holds).  Lane k < R of a group reads the index of the group's k-th row of the round and issues
-// that row's bulk copy into slot k*G + g (a lane whose row is not to be added -- index -1, or past the
-// group's range -- clears the slot's header, or the whole slot for a type without header, instead).
-// When the round's rows have landed the group reads them back, one per pass: 16 (INT4: 8) bytes per
-// lane, the header word by broadcast, and for INT8/INT4 the row's last 4 / 8 elements, which the lane
-// that owns the header chunk takes into the slots the header leaves free.  Interleaving the slots by
-// group keeps the G header words of a pass in different banks.  The indices of a round are requested
-// one round ahead, so only the first index load of a step is exposed.  (Two rounds of rows in flight per
-// warp, half the rows each, measured slower: the kernel is bound by instruction issue, and shorter
-// rounds mean more per-round work.)
-// FOLD (INT8, unweighted, 16-bit output): the subtraction of the magic constant that turns a code into
-// an fp16 value is skipped, (1024 + q) * scale is accumulated, and 1024 * sum(scale) is removed again at
-// least every 32 rows, which keeps the partial sums small enough for the extra term not to cost
-// precision that a 16-bit result could show.
-// Returns false when a wait for staged rows ran out (reported through the error flag, bit 1).
-template <int TY, int LPR, typename IdxT, bool WEIGHTED, bool FOLD>
-__device__ __noinline__ bool pool_run_staged(const LookupParams& p, const TableMeta& m, int64_t i0, int64_t i1, int64_t b0,
-                                             int lane, uint32_t wsm, uint32_t bar, uint32_t& parity)
+__host__ __device__ constexpr int floor_pow2(int x) { return x >= 8 ? 8 : x >= 4 ? 4 : x >= 2 ? 2 : 1; }
+__host__ __device__ constexpr int min3(int a, int b, int c) { return a < b ? (a < c ? a : c) : (b < c ? b : c); }
+
+// A run of nb <= kMaxRunBags consecutive bags of ONE table whose rows are D = 16 * n <= 512 elements, 16-byte
+// aligned.  LPR lanes share a row, 16 elements per lane, so a warp has G = 32 / LPR lane groups.
+//
+// Work split.  The run's rows -- positions [R0, R1) of `indices` -- are cut into G equal ranges, one per
+// group, whatever the bag lengths are, so the groups finish together.  A group walks its range row by row
+// and keeps the sum of the bag it is in; when the walk reaches the end of a bag the group stores the bag
+// and starts the next one (a divergent branch, taken once per bag and group).  A bag that straddles a range
+// boundary is summed in pieces: the group in whose range the bag STARTS owns it; every later group that holds
+// a piece writes its partial sum to shared memory, and the owner adds those pieces at the end of the run.
+// Empty bags are written (zeros) by the group whose walk passes their position.
+//
+// Row fetch.  Lane k of a group reads the index of the group's row c * LPR + k (chunk c of the range; the indices
+// of a chunk are requested two chunks ahead).  Rows travel through a ring of NS stages in the warp's shared memory:
+// in step q the group consumes row q - NS out of stage q mod NS and then requests row q into the same stage with
+// asynchronous copies (cp.async through L1, 16 bytes per lane, completion counted per step with commit / wait
+// groups), so NS rows per group are in flight all the time, whatever the compiler does with registers -- a ring of
+// registers filled by ordinary loads measured twice as slow, because a warp has only six scoreboards and a row
+// about to be consumed ended up waiting for loads that had just been issued.  A lane reads back only the bytes it
+// copied itself, so no barrier is involved.  A row that is not to be added (index -1, out of range, past the end
+// of the group's range) is zero-filled in the stage without being read.
+//
+// FOLD (INT8, unweighted, 16-bit output): the subtraction of the magic constant that turns a code into an fp16
+// value is skipped, (1024 + q) * scale is accumulated, and 1024 * sum(scale) is removed again at least every
+// 32 rows, which keeps the partial sums small enough for the extra term not to cost precision that a 16-bit
+// result could show.
+template <int TY, int LPR, int EPL, bool WEIGHTED, bool FOLD>
+__device__ __noinline__ void pool_run_stream(const LookupParams& p, const TableMeta& m, int64_t i0, int nb, int64_t b0, int lane,
+                                             uint32_t wsm)
 {
     static_assert(!FOLD || (TY == TBE_B200_INT8 && !WEIGHTED), "the folded form is for unweighted INT8 pooling");
+    static_assert(EPL == 16 || (EPL == 32 && (TY == TBE_B200_INT8 || TY == TBE_B200_INT4)), "32 elements per lane: INT8 / INT4 only");
     constexpr bool kHdr = (TY == TBE_B200_INT8 || TY == TBE_B200_INT4);
     constexpr bool k8 = (TY == TBE_B200_INT8);
-    constexpr int CH = (TY == TBE_B200_INT4) ? 8 : 16;                 // bytes per chunk read by a lane
-    constexpr int NCH = (TY == TBE_B200_FP16) ? 2 : (TY == TBE_B200_FP32) ? 4 : 1;   // chunks per lane and row
-    constexpr int EPC = 16 / NCH;                      // elements per chunk
+    // A lane holds NCH chunks of CH bytes of a row; chunk c is unit k + c * nunits of the row (a unit = UE elements),
+    // so one copy instruction of a group covers nunits * CH contiguous bytes.
+    constexpr int NCH = (TY == TBE_B200_FP16) ? 2 : (TY == TBE_B200_FP32) ? 4 : (k8 ? EPL / 16 : 1);
+    constexpr int CH = (TY == TBE_B200_INT4) ? EPL / 2 : 16;           // bytes per chunk
+    constexpr int UE = EPL / NCH;                      // elements per unit
     constexpr int HS = k8 ? 4 : (TY == TBE_B200_INT4 ? 8 : 0);         // slots of the header lane that hold the row's tail
-    constexpr int G = kWarp / LPR;                     // lane groups = rows per pass of the warp
+    constexpr int G = kWarp / LPR;                     // lane groups
     constexpr int LOG_G = G == 1 ? 0 : G == 2 ? 1 : G == 4 ? 2 : 3;
-    constexpr int NF = 16 / G;                         // split form: finished slots per lane after the reduce-scatter
-    constexpr int WS = NF >= 4 ? 4 : NF;               // split form: elements per store
+    constexpr int LANEB = CH * NCH;                                    // bytes of a row that one lane holds
+    constexpr int STAGE = kWarp * LANEB + (kHdr ? 32 : 0);             // one row per group, and the groups' tail words
+    constexpr int NS = floor_pow2(min3(kRingBytes / STAGE, LPR, TBE_MAX_STAGES));   // stages of the ring (rows in flight per group)
+    static_assert(NS >= 1 && NS * STAGE <= kRingBytes, "the ring does not fit");
     static_assert(G <= 8, "at least 4 lanes per row");
     const int k = lane % LPR;
     const int g = lane / LPR;
+    const unsigned gmask = (LPR == 32) ? kFull : (((1u << (LPR & 31)) - 1u) << (g * LPR));
     const int D = m.D;
-    const int nunits = D / 16;
+    const int nunits = D / EPL;                        // lanes that hold a piece of the row
     const bool head_lane = kHdr && (k == 0);
-    const bool active = k < nunits;                    // lanes past the row's last unit have nothing to add (D < 16 * LPR)
+    const bool act = k < nunits;                       // lanes past the row's last unit have nothing to add (D < EPL * LPR)
     const uint32_t stride = static_cast<uint32_t>(m.stride);
-    const uint32_t copy_bytes = static_cast<uint32_t>(row_bytes_of(TY, D, 16));   // the row without its alignment padding
-    const int R = min(LPR, (kStageBytes / static_cast<int>(copy_bytes)) >> LOG_G);   // rows per group and round (>= 1)
-    const uint32_t own_slot = wsm + static_cast<uint32_t>(k * G + g) * copy_bytes;   // the slot this lane fills (k < R)
-    const uint32_t read0 = wsm + static_cast<uint32_t>(g) * copy_bytes + (active ? k * CH : 0);   // pass 0, chunk 0
-    const uint32_t pass_pitch = G * copy_bytes;
-    // INT8/INT4: the extra word of a pass is the row's tail for the header lane and the header for the others.
-    const uint32_t extra0 = wsm + static_cast<uint32_t>(g) * copy_bytes + (head_lane ? (k8 ? D : D / 2) : 0);
-    const IdxT* offs = static_cast<const IdxT*>(p.offsets) + i0;
-    const IdxT* indices = static_cast<const IdxT*>(p.indices);
-    const int nb = static_cast<int>(i1 - i0);
-    const int esz = (p.out_ty == TBE_B200_FP32) ? 4 : 2;
-    const int64_t row_bytes = p.out_stride * esz;
-    const bool mean = p.pooling_mode == TBE_B200_POOL_MEAN;
-    char* out_run = nullptr;               // output address of (bag b0, first column of this table)
-    bool vec_ok = false;
-    if (!p.dests) {
-        out_run = static_cast<char*>(p.output) + m.col * esz + b0 * row_bytes;
-        vec_ok = ((reinterpret_cast<uintptr_t>(out_run) | static_cast<uint64_t>(row_bytes)) & 15) == 0;
+    const uint8_t* lane_base = m.table + k * CH;
+    const uint32_t tail_off = k8 ? D : D / 2;          // header lane (k = 0): where the row's last HS elements are
+    const uint32_t chunk_step = static_cast<uint32_t>(nunits) * CH;    // distance between a lane's chunks
+    const uint8_t* zero_base = g_zero_row + k * 16;
+    const bool idx64 = p.idx64 != 0;
+    const int isz = idx64 ? 8 : 4;
+    const uint32_t sm_rel = wsm + kPartBytes;
+
+    // The run's nb + 1 offsets, one per lane, relative to the first one.
+    int64_t off = 0;
+    if (lane <= nb) {
+        const char* op = static_cast<const char*>(p.offsets) + (i0 + lane) * isz;
+        off = idx64 ? __ldg(reinterpret_cast<const int64_t*>(op)) : static_cast<int64_t>(__ldg(reinterpret_cast<const int32_t*>(op)));
     }
-    // Element a slot stands for.  Chunk c = k + (slot / EPC) * nunits of the row holds EPC elements; INT8/INT4
-    // chunks are shifted by the header (unit k covers elements [16k - HS, 16k + 16 - HS)), and the header
-    // lane's first HS slots are the row's last HS elements.
+    const int64_t R0 = __shfl_sync(kFull, off, 0);
+    const int64_t R1 = __shfl_sync(kFull, off, nb);
+    if (R0 < 0 || R1 < R0 || R1 > p.num_indices || R1 - R0 > 0x7fffffffll) {
+        // Offsets that do not describe positions of `indices`: nothing is read through them.
+        if (p.error_flag && lane == 0) atomicOr(p.error_flag, 8);
+        return;
+    }
+    const int n = static_cast<int>(R1 - R0);
+    const int rel = static_cast<int>(min(max(off - R0, static_cast<int64_t>(0)), static_cast<int64_t>(n)));
+    __syncwarp();                                      // the previous run's reads of this memory are over
+    if (lane <= nb) sts4(sm_rel + 4 * lane, rel);
+    __syncwarp();
+
+    // This group's range of rows, and the bag its first row is in.
+    const int per = (n + G - 1) >> LOG_G;
+    const int lo = min(n, g * per);
+    const int hi = min(n, lo + per);
+    int cur = 0;
+    if constexpr (G > 1) {
+#pragma unroll
+        for (int gg = 1; gg < G; ++gg) {
+            const int lo_gg = min(n, gg * per);
+            const unsigned started = __ballot_sync(kFull, lane >= 1 && lane <= nb && rel <= lo_gg);
+            if (g == gg) cur = __popc(started);
+        }
+    }
+    const bool active = (g == 0) || (lo < hi);         // group 0 also writes the empty bags at the front of the run
+    int bag_start = lds4i(sm_rel + 4 * cur);
+    int bag_end = (active && cur < nb) ? lds4i(sm_rel + 4 * (cur + 1)) : -1;
+    int pos = lo;
+
+    // Element a slot stands for: slot s belongs to the lane's chunk s / UE, which is unit k + (s / UE) * nunits of the
+    // row.  INT8 / INT4 units are shifted by the header (unit u covers elements [UE * u - HS, UE * u + UE - HS)), and
+    // the header lane's first HS slots are the row's last HS elements.
     auto elem_of = [&](int slot) -> int {
-        if constexpr (kHdr) return (head_lane && slot < HS) ? (D - HS + slot) : (16 * k - HS + slot);
-        else return EPC * (k + (slot / EPC) * nunits) + (slot % EPC);
+        if (kHdr && head_lane && slot < HS) return D - HS + slot;
+        return UE * (k + (slot / UE) * nunits) - HS + (slot % UE);
     };
-    // Split form: which of its 16 slots a lane ends up with.
-    int slot_base = 0;
-    if constexpr (G >= 2) slot_base += ((lane >> 4) & 1) ? 8 : 0;
-    if constexpr (G >= 4) slot_base += ((lane >> 3) & 1) ? 4 : 0;
-    if constexpr (G >= 8) slot_base += ((lane >> 2) & 1) ? 2 : 0;
 
-    for (int j = 0; j < nb;) {
-        // Group g looks at bag j + g (an empty one past the end of the run).
-        const int64_t o0 = static_cast<int64_t>(__ldg(offs + min(j + g, nb)));
-        const int64_t o1 = static_cast<int64_t>(__ldg(offs + min(j + g + 1, nb)));
-        const int Lg = static_cast<int>(o1 - o0);
-        int maxL = Lg, sumL = Lg;
+    float acc[EPL];
 #pragma unroll
-        for (int d = LPR; d < kWarp; d <<= 1) {
-            maxL = max(maxL, __shfl_xor_sync(kFull, maxL, d));
-            sumL += __shfl_xor_sync(kFull, sumL, d);
-        }
-        // Side by side costs max(L) passes; one bag at a time costs about L / G + 4 passes per bag.
-        const int bags_here = min(G, nb - j);
-        const bool split = (G > 1) && (maxL + 2 > (sumL >> LOG_G) + 4 * bags_here);
-        int64_t lo = o0;      // this group's rows are indices[lo .. lo + n)
-        int n = Lg;
-        int maxn = maxL;      // rows of the longest group
-        int Lbag = Lg;        // length of the bag this lane contributes to
-        if (split) {
-            Lbag = __shfl_sync(kFull, Lg, 0);
-            const int64_t start = __shfl_sync(kFull, o0, 0);
-            const int per = (Lbag + G - 1) >> LOG_G;
-            const int a = min(Lbag, g * per);
-            lo = start + a;
-            n = min(Lbag, a + per) - a;
-            maxn = per;
-        }
-        const IdxT* ip = indices + lo + k;
-        const float* wp = WEIGHTED ? p.pw + lo + k : nullptr;
-        const int nrounds = (maxn + R - 1) / R;
+    for (int s = 0; s < EPL; ++s) acc[s] = 0.0f;
+    float bias_acc = 0.0f;
+    float scale_acc = 0.0f;   // sum of the row scales since the last fold (FOLD only)
+    int since_fold = 0;
+    (void)scale_acc;
+    (void)since_fold;
 
-        // Lane k < R of the group takes row r*R + k of round r.  The raw index is kept as loaded and only
-        // looked at when the round is issued, one iteration later, so the load has that long to arrive.
-        auto load_raw = [&](int r, IdxT& raw, float& w) {
-            raw = static_cast<IdxT>(-1);
-            w = 0.0f;
-            if (k < R && r * R + k < n) {
-                raw = __ldg(ip + r * R);
-                if constexpr (WEIGHTED) w = __ldg(wp + r * R);
-            }
-        };
-        // Index narrowed to 32 bits, -1 = nothing to add.
-        auto narrow = [&](IdxT raw) -> int32_t {
-            const bool bad = (raw < static_cast<IdxT>(-1)) || (sizeof(IdxT) == 8 && static_cast<int64_t>(raw) > 0x7fffffffll);
-            if (bad) {
-                if (p.error_flag) atomicOr(p.error_flag, 1);
-                return -1;
-            }
-            return static_cast<int32_t>(raw);
-        };
-        // Starts a round: the copy of this lane's row into its slot, or a cleared slot.
-        auto issue = [&](int32_t idx) {
-            const uint32_t slot = own_slot;
-            const uint32_t sbar = bar;
-            // The reads of the previous round (by every lane) come before the writes of this round.
-            __syncwarp();
-            fence_async_smem();
-            if (idx >= 0) {
-                mbar_arrive_expect(sbar, copy_bytes);
-                bulk_copy_row(slot, m.table + static_cast<uint64_t>(static_cast<uint32_t>(idx)) * stride, copy_bytes, sbar);
-            } else {
-                if (k < R) {
-                    if constexpr (kHdr) {
-                        asm volatile("st.shared.b32 [%0], %1;" ::"r"(slot), "r"(0u) : "memory");
+    // Stores the finished bag `bag` of L rows (acc + bias_acc, times 1/L for MEAN).  Executed by whole groups.
+    auto store_bag = [&](int bag, int L) {
+        const float mm = (p.pooling_mode == TBE_B200_POOL_MEAN && L > 0) ? 1.0f / static_cast<float>(L) : 1.0f;
+        const float bm = bias_acc * mm;
+        // (computed here, once per bag, rather than kept in registers across the row loop)
+        const int esz = (p.out_ty == TBE_B200_FP32) ? 4 : 2;
+        char* seg = p.dests ? dest_segment(p, b0 + bag, m.col, esz)
+                            : static_cast<char*>(p.output) + ((b0 + bag) * p.out_stride + m.col) * esz;
+        const bool vec = (reinterpret_cast<uintptr_t>(seg) & 15) == 0;
+        bool stored = false;
+        if constexpr (FOLD) {
+            // Unweighted INT8 with a 16-bit output.  A unit's 16 elements start 4 elements before a 32-byte boundary.
+            // Its first 4 go to the unit before it (unit 0's, the row's tail, to the last unit), after which every
+            // unit is 16 elements from a 32-byte boundary on: two aligned 16-byte stores, whole sectors.  The unit after
+            // lane k's chunk c is lane k + 1's chunk c, or, for the last lane, lane 0's NEXT chunk.  `vec` is the same
+            // for all lanes of the group, so the group takes the shuffles together.
+            if (vec) {
+                uint32_t h[EPL / 2];
+#pragma unroll
+                for (int q = 0; q < EPL / 2; ++q) {
+                    const float lo16 = fmaf(acc[2 * q], mm, bm), hi16 = fmaf(acc[2 * q + 1], mm, bm);
+                    if (p.out_ty == TBE_B200_FP16) {
+                        const __half2 hh = __floats2half2_rn(lo16, hi16);
+                        h[q] = *reinterpret_cast<const uint32_t*>(&hh);
                     } else {
-                        for (uint32_t o = 0; o < copy_bytes; o += 16)
-                            asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(slot + o), "r"(0u) : "memory");
+                        const __nv_bfloat162 bb = __floats2bfloat162_rn(lo16, hi16);
+                        h[q] = *reinterpret_cast<const uint32_t*>(&bb);
                     }
                 }
-                mbar_arrive(sbar);
-            }
-        };
-
-        float acc[16];
+                const int from = (k + 1 == nunits) ? 0 : k + 1;
 #pragma unroll
-        for (int s = 0; s < 16; ++s) acc[s] = 0.0f;
-        float bias_acc = 0.0f;
-        float scale_acc = 0.0f;   // sum of the row scales since the last fold (FOLD only)
-        int since_fold = 0;
-        (void)scale_acc;
-        (void)since_fold;
-
-        IdxT raw_next;
-        float w_cur = 0.0f, w_next = 0.0f;
-        if (nrounds > 0) {
-            IdxT raw0;
-            load_raw(0, raw0, w_cur);
-            load_raw(1, raw_next, w_next);
-            const int32_t idx0 = narrow(raw0);
-            if (idx0 < 0) w_cur = 0.0f;
-            issue(idx0);
-        }
-#pragma unroll 1
-        for (int r = 0; r < nrounds; ++r) {
-            if (!mbar_wait(bar, parity)) {
-                if (p.error_flag) atomicOr(p.error_flag, 2);
-                return false;
-            }
-            parity ^= 1u;
-
-            const int cnt = min(R, maxn - r * R);
-            uint32_t rd = read0, ex = extra0;
-#pragma unroll 1
-            for (int u = 0; u < cnt; ++u, rd += pass_pitch, ex += pass_pitch) {
-                float w = 1.0f;
-                if constexpr (WEIGHTED) w = __shfl_sync(kFull, w_cur, u, LPR);
-                if constexpr (kHdr) {
-                    uint32_t words[4] = {0u, 0u, 0u, 0u};
-                    if (k8) {
-                        const uint4 v = lds16(rd);
-                        words[0] = v.x; words[1] = v.y; words[2] = v.z; words[3] = v.w;
-                    } else {
-                        const uint2 v = lds8(rd);
-                        words[0] = v.x; words[1] = v.y;
-                    }
-                    const uint32_t x = lds4(ex);
-                    const uint32_t hdr = head_lane ? words[0] : x;
-                    const uint32_t w0 = head_lane ? x : words[0];
-                    accum_header_row<TY, WEIGHTED, FOLD>(w0, words, hdr, w, acc, bias_acc, scale_acc);
-                } else if constexpr (TY == TBE_B200_FP8) {
-                    // byte -> fp32 by bit placement: ((b & 0x7f) << (16 + ebits)) as a float, times 2^(127 - bias),
-                    // sign bit or'ed in (reference: c310/op_kernel/common.h:120-167)
-                    const uint4 v = lds16(rd);
-                    const uint32_t words[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-                    for (int i4 = 0; i4 < 4; ++i4) {
-#pragma unroll
-                        for (int b4 = 0; b4 < 4; ++b4) {
-                            const uint32_t by = (words[i4] >> (8 * b4)) & 0xffu;
-                            const float mag = __uint_as_float((by & 0x7fu) << p.fp8_shift) * p.fp8_mult;
-                            const float val = __uint_as_float(__float_as_uint(mag) | ((by & 0x80u) << 24));
-                            acc[4 * i4 + b4] = fmaf(w, val, acc[4 * i4 + b4]);
-                        }
-                    }
-                } else if constexpr (TY == TBE_B200_FP16) {
-#pragma unroll
-                    for (int c = 0; c < 2; ++c) {
-                        const uint4 v = lds16(rd + c * nunits * 16);
-                        const uint32_t words[4] = {v.x, v.y, v.z, v.w};
-                        // unweighted: value * 1.0 + acc in one mixed FMA
-#pragma unroll
-                        for (int i4 = 0; i4 < 4; ++i4)
-                            add_pair_t<WEIGHTED>(acc[8 * c + 2 * i4], acc[8 * c + 2 * i4 + 1], words[i4], 0x3c00u, w);
-                    }
-                } else {
-#pragma unroll
-                    for (int c = 0; c < 4; ++c) {
-                        const uint4 v = lds16(rd + c * nunits * 16);
-                        acc[4 * c + 0] = fmaf(w, __uint_as_float(v.x), acc[4 * c + 0]);
-                        acc[4 * c + 1] = fmaf(w, __uint_as_float(v.y), acc[4 * c + 1]);
-                        acc[4 * c + 2] = fmaf(w, __uint_as_float(v.z), acc[4 * c + 2]);
-                        acc[4 * c + 3] = fmaf(w, __uint_as_float(v.w), acc[4 * c + 3]);
+                for (int c = 0; c < NCH; ++c) {
+                    const int cn = (c + 1) % NCH;
+                    const uint32_t s0 = (k == 0) ? h[8 * cn] : h[8 * c];
+                    const uint32_t s1 = (k == 0) ? h[8 * cn + 1] : h[8 * c + 1];
+                    const uint32_t up0 = __shfl_sync(gmask, s0, from, LPR);
+                    const uint32_t up1 = __shfl_sync(gmask, s1, from, LPR);
+                    if (act) {
+                        char* dst = seg + 32 * (k + c * nunits);
+                        st_stream16(dst, make_uint4(h[8 * c + 2], h[8 * c + 3], h[8 * c + 4], h[8 * c + 5]));
+                        st_stream16(dst + 16, make_uint4(h[8 * c + 6], h[8 * c + 7], up0, up1));
                     }
                 }
-            }
-            if constexpr (FOLD) {
-                since_fold += cnt;
-                if (since_fold >= 32) {
-#pragma unroll
-                    for (int s = 0; s < 16; ++s) acc[s] = fmaf(-1024.0f, scale_acc, acc[s]);
-                    scale_acc = 0.0f;
-                    since_fold = 0;
-                }
-            }
-            if (r + 1 < nrounds) {
-                // The next round's rows go out (its indices were requested a round ago), then the request for
-                // the indices of the round after it.
-                const int32_t idx1 = narrow(raw_next);
-                w_cur = (idx1 >= 0) ? w_next : 0.0f;
-                issue(idx1);
-                load_raw(r + 2, raw_next, w_next);
+                stored = true;
             }
         }
-        // What is left of the folded offset goes out with the biases.
-        if constexpr (FOLD) bias_acc = fmaf(-1024.0f, scale_acc, bias_acc);
-        const float mean_mul = (mean && Lbag > 0) ? 1.0f / static_cast<float>(Lbag) : 1.0f;
-
-        if (!split) {
-            // Every group stores its own bag: slots [4q, 4q + 4) of a lane are 4 consecutive elements.
-            const int64_t bag = j + g;
-            char* seg = p.dests ? dest_segment(p, b0 + bag, m.col, esz) : out_run + bag * row_bytes;
-            const bool vec = p.dests ? (reinterpret_cast<uintptr_t>(seg) & 15) == 0 : vec_ok;
-            bool stored = false;
+        if (!stored && act) {
+#pragma unroll
+            for (int q = 0; q < EPL / 4; ++q) {
+                float v[4];
+#pragma unroll
+                for (int s = 0; s < 4; ++s) v[s] = fmaf(acc[4 * q + s], mm, bm);
+                store_out<4>(seg, elem_of(4 * q), v, p.out_ty, vec);
+            }
+        }
+    };
+    // Hands this group's piece of a bag that started in an earlier group's range to that bag's owner.
+    auto write_partial = [&]() {
+#pragma unroll
+        for (int q = 0; q < EPL / 4; ++q)
+            sts16(wsm + static_cast<uint32_t>(q * kWarp + lane) * 16u, acc[4 * q + 0] + bias_acc, acc[4 * q + 1] + bias_acc,
+                  acc[4 * q + 2] + bias_acc, acc[4 * q + 3] + bias_acc);
+    };
+    // Finishes every bag that ends at the group's position (the one being summed, then the empty ones after it).
+    auto drain = [&]() {
+        while (pos == bag_end) {
             if constexpr (FOLD) {
-                // Unweighted INT8 with a 16-bit output (the only instantiation that carries this code: compiled into
-                // the others it cost the INT4 and fp32-output shapes 4 % through register allocation alone).  A
-                // lane's 16 elements start 4 elements before a 32-byte boundary.  Its first 4 go to the lane below
-                // (the header lane's, the row's tail, to the last lane), after which every lane owns elements
-                // [16k, 16k + 16): two aligned 16-byte stores, whole sectors, instead of four 8-byte ones that share
-                // sectors with the neighbours.
-                if (vec) {
-                    uint32_t h[8];
-#pragma unroll
-                    for (int q = 0; q < 8; ++q) {
-                        const float lo16 = (acc[2 * q] + bias_acc) * mean_mul, hi16 = (acc[2 * q + 1] + bias_acc) * mean_mul;
-                        h[q] = (p.out_ty == TBE_B200_FP16) ? (f32_to_f16_bits(lo16) | (f32_to_f16_bits(hi16) << 16))
-                                                           : (f32_to_bf16_bits(lo16) | (f32_to_bf16_bits(hi16) << 16));
-                    }
-                    const int from = (k + 1 == nunits) ? 0 : k + 1;
-                    const uint32_t up0 = __shfl_sync(kFull, h[0], from, LPR);
-                    const uint32_t up1 = __shfl_sync(kFull, h[1], from, LPR);
-                    if (active && bag < nb) {
-                        st_stream16(seg + 32 * k, make_uint4(h[2], h[3], h[4], h[5]));
-                        st_stream16(seg + 32 * k + 16, make_uint4(h[6], h[7], up0, up1));
-                    }
-                    stored = true;
-                }
+                bias_acc = fmaf(-1024.0f, scale_acc, bias_acc);
+                scale_acc = 0.0f;
             }
-            if (!stored && active && bag < nb) {
+            if (bag_start < lo) write_partial();
+            else store_bag(cur, bag_end - bag_start);
 #pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                    float v[4];
-#pragma unroll
-                    for (int s = 0; s < 4; ++s) v[s] = (acc[4 * q + s] + bias_acc) * mean_mul;
-                    store_out<4>(seg, elem_of(4 * q), v, p.out_ty, vec);
-                }
-            }
-            j += G;
+            for (int s = 0; s < EPL; ++s) acc[s] = 0.0f;
+            bias_acc = 0.0f;
+            ++cur;
+            bag_start = bag_end;
+            bag_end = (cur < nb) ? lds4i(sm_rel + 4 * (cur + 1)) : -1;
+        }
+    };
+    drain();
+
+    // Index stream of the group: lane k reads the index (and weight) of row c * LPR + k of the range (chunk c).
+    const char* ipb = static_cast<const char*>(p.indices) + (R0 + lo + k) * isz;
+    const float* wpb = WEIGHTED ? p.pw + R0 + lo + k : nullptr;
+    auto load_raw = [&](int c, int64_t& raw, float& w) {
+        raw = -1;
+        w = 0.0f;
+        if (lo + c * LPR + k < hi) {
+            const char* ip = ipb + static_cast<int64_t>(c) * (LPR * isz);
+            raw = idx64 ? ld_once64(ip) : static_cast<int64_t>(ld_once32(ip));
+            if constexpr (WEIGHTED) w = ld_once_f32(wpb + c * LPR);
+        }
+    };
+    // Row number narrowed to 32 bits; -1 = nothing to add.  A row outside [-1, 2^31) or past the end of the
+    // table is reported and skipped.
+    const uint64_t avail = static_cast<uint64_t>(m.avail);
+    auto narrow = [&](int64_t raw) -> int32_t {
+        if (raw == -1) return -1;
+        const bool bad_range = raw < -1 || raw > 0x7fffffffll;
+        const bool bad_row = !bad_range && static_cast<uint64_t>(raw + 1) * stride > avail;
+        if (bad_range || bad_row) {
+            if (p.error_flag) atomicOr(p.error_flag, bad_range ? 1 : 4);
+            return -1;
+        }
+        return static_cast<int32_t>(raw);
+    };
+
+    // The ring of rows in flight: stage s holds one row per group; a lane copies and reads back its own chunk(s)
+    // only (chunk c of lane l at (c * 32 + l) * 16), the header lane also the group's tail word.
+#ifdef TBE_L2_HINTS
+    const uint64_t row_policy = l2_policy_evict_last();
+#endif
+    const uint32_t ring = wsm + kPartBytes + kRelBytes;
+    const uint32_t my_main = ring + static_cast<uint32_t>(lane) * CH;   // chunk c of lane l at (c * 32 + l) * CH
+    const uint32_t my_tail = ring + kWarp * LANEB + static_cast<uint32_t>(g) * 4u;
+    // Requests row `idx` of the table into stage `st` (byte offset): asynchronous copies through L1, zero-filled
+    // without reading for a row that is not to be added.
+    auto request = [&](uint32_t st, int32_t idx) {
+        const bool ok = act && idx >= 0;   // the lanes past the row's last unit zero-fill their slots as well
+        const uint8_t* src = ok ? lane_base + static_cast<uint64_t>(static_cast<uint32_t>(idx)) * stride : zero_base;
+        const int sz = ok ? CH : 0;
+        if constexpr (CH == 8) {
+            cp_async8(my_main + st, src, sz);
         } else {
-            // One bag over all groups: reduce-scatter the partial sums, add the pooled biases, store.
-            if constexpr (G >= 2) halve<16>(acc, 16, (lane >> 4) & 1);
-            if constexpr (G >= 4) halve<8>(acc, 8, (lane >> 3) & 1);
-            if constexpr (G >= 8) halve<4>(acc, 4, (lane >> 2) & 1);
-            if constexpr (kHdr) {
 #pragma unroll
-                for (int d = LPR; d < kWarp; d <<= 1) bias_acc += __shfl_xor_sync(kFull, bias_acc, d);
+            for (int c = 0; c < NCH; ++c) {
+#ifdef TBE_L2_HINTS
+                cp_async16_ca_hint(my_main + st + c * (kWarp * 16), src + c * chunk_step, sz, row_policy);
+#else
+                cp_async16_ca(my_main + st + c * (kWarp * 16), src + c * chunk_step, sz);
+#endif
             }
-            char* seg = p.dests ? dest_segment(p, b0 + j, m.col, esz) : out_run + static_cast<int64_t>(j) * row_bytes;
-            const bool vec = p.dests ? (reinterpret_cast<uintptr_t>(seg) & 15) == 0 : vec_ok;
-            if (active) {
+        }
+        if constexpr (kHdr) {
+            if (head_lane) cp_async4(my_tail + st, src + tail_off, ok ? 4 : 0);   // (zero_base + tail_off is still inside the zeros)
+        }
+        cp_async_commit();
+    };
+    // Adds the row in stage `st`, with weight w.
+    auto consume = [&](uint32_t st, float w) {
+        constexpr int NW = LANEB / 4;      // 32-bit words of the row in this lane
+        uint32_t r[NW];
+        if constexpr (CH == 8) {
+            const uint2 v = lds8(my_main + st);
+            r[0] = v.x;
+            r[1] = v.y;
+        } else {
 #pragma unroll
-                for (int q = 0; q < NF / WS; ++q) {
-                    float v[WS];
+            for (int c = 0; c < NCH; ++c) {
+                const uint4 v = lds16(my_main + st + c * (kWarp * 16));
+                r[4 * c + 0] = v.x;
+                r[4 * c + 1] = v.y;
+                r[4 * c + 2] = v.z;
+                r[4 * c + 3] = v.w;
+            }
+        }
+        if constexpr (kHdr) {
+            const uint32_t hdr = __shfl_sync(kFull, r[0], 0, LPR);   // zero for a row that was not copied
+            if (head_lane) r[0] = lds4(my_tail + st);                // the header lane's first HS slots: the row's tail
+            float ws;
+            const unsigned short scale_h = accum_header<WEIGHTED, FOLD>(hdr, w, ws, bias_acc, scale_acc);
+            accum_codes<TY, WEIGHTED, FOLD, NW>(r, scale_h, ws, acc);
+        } else if constexpr (TY == TBE_B200_FP8) {
+            // byte -> fp32 by bit placement: ((b & 0x7f) << (16 + ebits)) as a float, times 2^(127 - bias),
+            // sign bit or'ed in (reference: c310/op_kernel/common.h:120-167)
 #pragma unroll
-                    for (int s = 0; s < WS; ++s) v[s] = (acc[q * WS + s] + bias_acc) * mean_mul;
-                    store_out<WS>(seg, elem_of(slot_base + q * WS), v, p.out_ty, vec);
+            for (int i4 = 0; i4 < 4; ++i4) {
+#pragma unroll
+                for (int b4 = 0; b4 < 4; ++b4) {
+                    const uint32_t by = (r[i4] >> (8 * b4)) & 0xffu;
+                    const float mag = __uint_as_float((by & 0x7fu) << p.fp8_shift) * p.fp8_mult;
+                    const float val = __uint_as_float(__float_as_uint(mag) | ((by & 0x80u) << 24));
+                    acc[4 * i4 + b4] = fmaf(w, val, acc[4 * i4 + b4]);
                 }
             }
-            j += 1;
+        } else if constexpr (TY == TBE_B200_FP16) {
+            // unweighted: value * 1.0 + acc in one mixed FMA
+#pragma unroll
+            for (int i8 = 0; i8 < 8; ++i8) add_pair_t<WEIGHTED>(acc[2 * i8], acc[2 * i8 + 1], r[i8], 0x3c00u, w);
+        } else {
+#pragma unroll
+            for (int s = 0; s < 16; ++s) acc[s] = fmaf(w, __uint_as_float(r[s]), acc[s]);
+        }
+    };
+
+    // Step q requests row q of the range and consumes row q - NS (copied NS steps ago into the same stage), so NS rows
+    // per group are in flight; rows per .. per + NS - 1 do not exist and only drain the ring.  The step loop is kept
+    // rolled on purpose: unrolled over the stages (constant stage addresses, one copy of the end-of-bag code per stage)
+    // it measured 5-10 % slower, and twice as slow with eight stages -- the loop no longer fits the instruction cache.
+    const int total = per + NS;
+    int64_t raw_a, raw_b;                  // the indices of the next chunk and of the one after it, as loaded
+    float w_a = 0.0f, w_b = 0.0f;
+    int32_t idx_c;                         // lane k: index of row c * LPR + k of the chunk being requested
+    float w_c = 0.0f, w_prev = 0.0f;       // weights of the chunk being requested / of the one before it
+    {
+        int64_t raw0;
+        load_raw(0, raw0, w_c);
+        load_raw(1, raw_a, w_a);
+        load_raw(2, raw_b, w_b);
+        idx_c = narrow(raw0);
+        if (idx_c < 0) w_c = 0.0f;
+    }
+    int q = 0;
+#pragma unroll 1
+    for (int c = 0; q < total; ++c) {
+        if (c > 0) {
+            w_prev = w_c;
+            idx_c = narrow(raw_a);
+            w_c = (idx_c >= 0) ? w_a : 0.0f;
+            raw_a = raw_b;
+            w_a = w_b;
+            load_raw(c + 2, raw_b, w_b);
+        }
+        const int u_end = min(LPR, total - q);
+#pragma unroll 1
+        for (int u = 0; u < u_end; ++u, ++q) {
+            const uint32_t st = static_cast<uint32_t>(q & (NS - 1)) * STAGE;
+            if (q >= NS) {
+                float w = 1.0f;
+                if constexpr (WEIGHTED) w = __shfl_sync(kFull, u >= NS ? w_c : w_prev, (u - NS) & (LPR - 1), LPR);
+                cp_async_wait<NS - 1>();
+                consume(st, w);
+                pos = min(pos + 1, hi);
+                if (pos == bag_end) drain();
+            }
+            request(st, __shfl_sync(kFull, idx_c, u, LPR));
+        }
+        if constexpr (FOLD) {
+            since_fold += u_end;
+            if (since_fold + LPR > 32) {
+#pragma unroll
+                for (int s = 0; s < EPL; ++s) acc[s] = fmaf(-1024.0f, scale_acc, acc[s]);
+                scale_acc = 0.0f;
+                since_fold = 0;
+            }
         }
     }
-    return true;
+    cp_async_wait<0>();                    // nothing of this run is still on its way when the ring is handed on
+
+    // A bag that the range ended in the middle of: a piece for its owner, or, when it started in this range, the
+    // owner's own piece, completed with the pieces of the groups after it.
+    const bool open = active && bag_end >= 0 && bag_start < pos && pos < bag_end;
+    if (open) {
+        if constexpr (FOLD) {
+            bias_acc = fmaf(-1024.0f, scale_acc, bias_acc);
+            scale_acc = 0.0f;
+        }
+        if (bag_start < lo) write_partial();
+    }
+    __syncwarp();
+    if (open && bag_start >= lo) {
+        for (int gg = g + 1; gg < G && gg * per < bag_end; ++gg) {
+#pragma unroll
+            for (int q = 0; q < EPL / 4; ++q) {
+                const float4 v = lds16f(wsm + static_cast<uint32_t>(q * kWarp + gg * LPR + k) * 16u);
+                acc[4 * q + 0] += v.x;
+                acc[4 * q + 1] += v.y;
+                acc[4 * q + 2] += v.z;
+                acc[4 * q + 3] += v.w;
+            }
+        }
+        store_bag(cur, bag_end - bag_start);
+    }
 }
 
+template <int TY, bool WEIGHTED, bool FOLD>
+__device__ __forceinline__ void pool_run_stream_by_width(const LookupParams& p, const TableMeta& m, int64_t i0, int nb, int64_t b,
+                                                         int lane, uint32_t wsm)
+{
+    // INT8 / INT4 rows of 128 elements or more that divide into 32-element pieces: 32 elements per lane, so that twice
+    // as many bags share a warp and the per-row work that does not depend on the width is shared twice as widely.
+    if constexpr (TY == TBE_B200_INT8 || TY == TBE_B200_INT4) {
+        if (m.D >= 128 && (m.D & 31) == 0) {
+            const int n32 = m.D / 32;
+            if (n32 <= 4) pool_run_stream<TY, 4, 32, WEIGHTED, FOLD>(p, m, i0, nb, b, lane, wsm);
+            else if (n32 <= 8) pool_run_stream<TY, 8, 32, WEIGHTED, FOLD>(p, m, i0, nb, b, lane, wsm);
+            else pool_run_stream<TY, 16, 32, WEIGHTED, FOLD>(p, m, i0, nb, b, lane, wsm);
+            return;
+        }
+    }
+    const int nunits = m.D / 16;
+    if (nunits <= 4) pool_run_stream<TY, 4, 16, WEIGHTED, FOLD>(p, m, i0, nb, b, lane, wsm);
+    else if (nunits <= 8) pool_run_stream<TY, 8, 16, WEIGHTED, FOLD>(p, m, i0, nb, b, lane, wsm);
+    else if (nunits <= 16) pool_run_stream<TY, 16, 16, WEIGHTED, FOLD>(p, m, i0, nb, b, lane, wsm);
+    else pool_run_stream<TY, 32, 16, WEIGHTED, FOLD>(p, m, i0, nb, b, lane, wsm);
+}
+
+#ifdef TBE_STREAM_BENCH_SHAPES_ONLY
+// Experiment builds: only the INT8 D <= 128 unweighted 16-bit-output stream is compiled; everything else must not be run.
+template <bool WEIGHTED>
+__device__ __forceinline__ void pool_run_stream_by_type(const LookupParams& p, const TableMeta& m, int64_t i0, int nb, int64_t b,
+                                                        int lane, uint32_t wsm)
+{
+    if constexpr (!WEIGHTED) {
+        if (m.ty == TBE_B200_INT8 && p.out_ty != TBE_B200_FP32 && m.D == 128) {
+#ifdef TBE_BENCH_EPL16
+            pool_run_stream<TBE_B200_INT8, 8, 16, false, true>(p, m, i0, nb, b, lane, wsm);
+#else
+            pool_run_stream<TBE_B200_INT8, 4, 32, false, true>(p, m, i0, nb, b, lane, wsm);
+#endif
+        }
+    }
+}
+#else
+template <bool WEIGHTED>
+__device__ __forceinline__ void pool_run_stream_by_type(const LookupParams& p, const TableMeta& m, int64_t i0, int nb, int64_t b,
+                                                        int lane, uint32_t wsm)
+{
+    switch (m.ty) {
+        case TBE_B200_INT8:
+            if constexpr (!WEIGHTED) {
+                if (p.out_ty != TBE_B200_FP32) {
+                    pool_run_stream_by_width<TBE_B200_INT8, false, true>(p, m, i0, nb, b, lane, wsm);
+                    return;
+                }
+            }
+            pool_run_stream_by_width<TBE_B200_INT8, WEIGHTED, false>(p, m, i0, nb, b, lane, wsm);
+            return;
+        case TBE_B200_INT4: pool_run_stream_by_width<TBE_B200_INT4, WEIGHTED, false>(p, m, i0, nb, b, lane, wsm); return;
+        case TBE_B200_FP8: pool_run_stream_by_width<TBE_B200_FP8, WEIGHTED, false>(p, m, i0, nb, b, lane, wsm); return;
+        case TBE_B200_FP16: pool_run_stream_by_width<TBE_B200_FP16, WEIGHTED, false>(p, m, i0, nb, b, lane, wsm); return;
+        default: pool_run_stream_by_width<TBE_B200_FP32, WEIGHTED, false>(p, m, i0, nb, b, lane, wsm); return;
+    }
+}
+#endif
+
+
 // A run of bags of one table through the general per-bag code.
-template <typename IdxT>
+template <typename IdxT, bool STAGING>
 __device__ __forceinline__ void pool_run_general(const LookupParams& p, const TableMeta& m, int64_t i0, int64_t i1, int64_t b,
                                                  int lane, uint32_t wsm)
 {
@@ -1181,6 +1359,7 @@ __device__ __forceinline__ void pool_run_general(const LookupParams& p, const Ta
         const int L = static_cast<int>(end - start);
         BagInfo bag;
         bag.table = m.table;
+        bag.avail = m.avail;
         bag.stride = m.stride;
         bag.start = start;
         bag.L = L;
@@ -1198,8 +1377,9 @@ __device__ __forceinline__ void pool_run_general(const LookupParams& p, const Ta
         bag.seg = dst + (brow * p.out_stride + m.col) * esz;
         bag.seg_aligned = (reinterpret_cast<uintptr_t>(bag.seg) & 15) == 0;
         bool done = false;
-        if (m.rows_aligned && (m.D & 3) == 0) {
-            const BagHead head = load_batch<IdxT>(indices + start, p.pw ? p.pw + start : nullptr, min(L, kWarp), lane, p.error_flag);
+        if (STAGING && m.rows_aligned && (m.D & 3) == 0 && L >= 0 && start >= 0 && end <= p.num_indices) {
+            const BagHead head = load_batch<IdxT>(indices + start, p.pw ? p.pw + start : nullptr, min(L, kWarp), lane, p.error_flag,
+                                                  m.stride, m.avail);
             done = true;
             switch (m.ty) {
                 case TBE_B200_INT8: pool_bag_by_width<TBE_B200_INT8, IdxT>(p, bag, head, lane, wsm); break;
@@ -1213,61 +1393,47 @@ __device__ __forceinline__ void pool_run_general(const LookupParams& p, const Ta
                 default: done = false; break;
             }
         }
-        if (!done)
-            pool_bag_bytewise<IdxT>(indices + start, p.pw ? p.pw + start : nullptr, p.error_flag, bag.table, bag.stride, L,
-                                    m.D, bag.seg, bag.mean_mul, m.ty, p.out_ty, p.fp8_shift, p.fp8_mult, lane);
+        if (!done) {
+            // positions outside `indices` are not read: the bag is written as if it were empty, and reported
+            const bool sane = L >= 0 && start >= 0 && end <= p.num_indices;
+            if (!sane && lane == 0 && p.error_flag) atomicOr(p.error_flag, 8);
+            pool_bag_bytewise<IdxT>(indices + start, p.pw ? p.pw + start : nullptr, p.error_flag, bag.table, bag.stride, sane ? L : 0,
+                                    m.D, bag.seg, bag.mean_mul, m.ty, p.out_ty, p.fp8_shift, p.fp8_mult, lane, m.avail);
+        }
         start = end;
-    }
-}
-
-template <int TY, typename IdxT, bool WEIGHTED, bool FOLD>
-__device__ __forceinline__ bool pool_run_staged_by_width(const LookupParams& p, const TableMeta& m, int64_t i0, int64_t i1,
-                                                         int64_t b, int lane, uint32_t wsm, uint32_t bar, uint32_t& parity)
-{
-    const int nunits = m.D / 16;
-    if (nunits <= 4) return pool_run_staged<TY, 4, IdxT, WEIGHTED, FOLD>(p, m, i0, i1, b, lane, wsm, bar, parity);
-    if (nunits <= 8) return pool_run_staged<TY, 8, IdxT, WEIGHTED, FOLD>(p, m, i0, i1, b, lane, wsm, bar, parity);
-    if (nunits <= 16) return pool_run_staged<TY, 16, IdxT, WEIGHTED, FOLD>(p, m, i0, i1, b, lane, wsm, bar, parity);
-    return pool_run_staged<TY, 32, IdxT, WEIGHTED, FOLD>(p, m, i0, i1, b, lane, wsm, bar, parity);
-}
-
-template <typename IdxT, bool WEIGHTED>
-__device__ __forceinline__ bool pool_run_staged_by_type(const LookupParams& p, const TableMeta& m, int64_t i0, int64_t i1,
-                                                        int64_t b, int lane, uint32_t wsm, uint32_t bar, uint32_t& parity)
-{
-    switch (m.ty) {
-        case TBE_B200_INT8:
-            if constexpr (!WEIGHTED) {
-                if (p.out_ty != TBE_B200_FP32)
-                    return pool_run_staged_by_width<TBE_B200_INT8, IdxT, false, true>(p, m, i0, i1, b, lane, wsm, bar, parity);
-            }
-            return pool_run_staged_by_width<TBE_B200_INT8, IdxT, WEIGHTED, false>(p, m, i0, i1, b, lane, wsm, bar, parity);
-        case TBE_B200_INT4: return pool_run_staged_by_width<TBE_B200_INT4, IdxT, WEIGHTED, false>(p, m, i0, i1, b, lane, wsm, bar, parity);
-        case TBE_B200_FP8: return pool_run_staged_by_width<TBE_B200_FP8, IdxT, WEIGHTED, false>(p, m, i0, i1, b, lane, wsm, bar, parity);
-        case TBE_B200_FP16: return pool_run_staged_by_width<TBE_B200_FP16, IdxT, WEIGHTED, false>(p, m, i0, i1, b, lane, wsm, bar, parity);
-        default: return pool_run_staged_by_width<TBE_B200_FP32, IdxT, WEIGHTED, false>(p, m, i0, i1, b, lane, wsm, bar, parity);
     }
 }
 
 // ---- kernels -----------------------------------------------------------------
 
 constexpr int kWarpsPerBlock = 4;
-constexpr int kMinBlocksPerSM = 8;   // 32 resident warps per SM: 64 registers and 6 KB of staging memory per warp
+#ifndef TBE_SPAN_LARGE
+#define TBE_SPAN_LARGE 31
+#endif
+#ifndef TBE_STREAM_BLOCKS_PER_SM
+#define TBE_STREAM_BLOCKS_PER_SM 4   // 16 resident warps per SM at up to 128 registers (32 accumulators per lane); measured best
+#endif
+constexpr int kStreamBlocksPerSM = TBE_STREAM_BLOCKS_PER_SM;
+constexpr int kWideBlocksPerSM = 8;
 
 // The T*B bags (bag i = t*B + b) are cut into spans of `span` consecutive bags, one span per warp, so a
 // warp walks `offsets`, `indices` and the per-sample weights front to back.  A span is processed as runs
 // of consecutive bags of one table: the table's description is read once per run and the run is handed
 // to the code specialised for its row shape.
-template <typename IdxT, int MINB>
-__global__ void __launch_bounds__(kWarpsPerBlock* kWarp, MINB)
+// Two builds of the kernel share this outline.  WIDE = false is the one for the common shapes: every table with
+// aligned rows of D = 16 * n <= 512 elements goes through the register streams (little shared memory, so most of
+// the SM's memory is L1 for the hot rows), anything else through the byte-wise path.  WIDE = true is launched when
+// the widest table has more than 512 elements or a width that is not a multiple of 16: aligned shapes use the
+// cp.async staging of pool_bag there.
+template <typename IdxT, bool WIDE>
+__global__ void __launch_bounds__(kWarpsPerBlock* kWarp, WIDE ? kWideBlocksPerSM : kStreamBlocksPerSM)
 tbe_pooled_kernel(const __grid_constant__ LookupParams p)
 {
-    __shared__ __align__(128) uint8_t smem[kWarpsPerBlock * kWarpSmemBytes];
-    __shared__ __align__(8) uint64_t bars[kWarpsPerBlock];
+    constexpr int kSmemPerWarp = WIDE ? kWarpSmemBytes : kStreamSmemBytes;
+    __shared__ __align__(128) uint8_t smem[kWarpsPerBlock * kSmemPerWarp];
     const int lane = threadIdx.x & 31;
     const int warp = threadIdx.x >> 5;
-    const uint32_t wsm = smem_u32(smem) + warp * kWarpSmemBytes;
-    const uint32_t bar = smem_u32(&bars[warp]);
+    const uint32_t wsm = smem_u32(smem) + warp * kSmemPerWarp;
     const int64_t gw = static_cast<int64_t>(blockIdx.x) * kWarpsPerBlock + warp;
     const int64_t span_lo = gw * p.span;
     const int64_t span_hi = min(p.num_bags, span_lo + p.span);
@@ -1278,10 +1444,11 @@ tbe_pooled_kernel(const __grid_constant__ LookupParams p)
         const IdxT* o = static_cast<const IdxT*>(p.offsets) + (lane == 0 ? span_lo : span_hi);
         asm volatile("prefetch.global.L1 [%0];" ::"l"(o));
     }
-    // One mbarrier per warp; every lane arrives once per round of staged rows.
-    if (lane == 0) mbar_init(bar, kWarp);
-    __syncwarp();
-    uint32_t parity = 0;
+    // The last offset has to be the number of indices (the reference kernel asserts the same:
+    // c310/op_kernel/int_nbit_split_embedding_pooling_kernel.h:149-150); here it is reported, not trapped.
+    if (gw == 0 && lane == 0 && p.error_flag) {
+        if (static_cast<int64_t>(static_cast<const IdxT*>(p.offsets)[p.num_bags]) != p.num_indices) atomicOr(p.error_flag, 8);
+    }
 
     int t;
     int64_t b;
@@ -1298,16 +1465,19 @@ tbe_pooled_kernel(const __grid_constant__ LookupParams p)
         const int64_t run_end = min(span_hi, i + (p.B - b));   // the bags left in table t, or in the span
         const TableMeta m = load_meta(p, t);
         if (m.D > 0) {
-            const bool staged = m.rows_aligned && (m.D & 15) == 0 && m.D <= 512 && m.stride < (1ll << 32) &&
-                                (m.ty == TBE_B200_INT8 || m.ty == TBE_B200_INT4 || m.ty == TBE_B200_FP8 ||
-                                 m.ty == TBE_B200_FP16 || m.ty == TBE_B200_FP32);
-            if (staged) {
-                const bool ok = weighted ? pool_run_staged_by_type<IdxT, true>(p, m, i, run_end, b, lane, wsm, bar, parity)
-                                         : pool_run_staged_by_type<IdxT, false>(p, m, i, run_end, b, lane, wsm, bar, parity);
-                if (!ok) return;   // a bounded wait ran out; the error flag says so
-            } else {
-                pool_run_general<IdxT>(p, m, i, run_end, b, lane, wsm);
+            bool done = false;
+            if constexpr (!WIDE) {
+                const bool stream = m.rows_aligned && (m.D & 15) == 0 && m.D <= 512 && m.stride < (1ll << 32) &&
+                                    (m.ty == TBE_B200_INT8 || m.ty == TBE_B200_INT4 || m.ty == TBE_B200_FP8 ||
+                                     m.ty == TBE_B200_FP16 || m.ty == TBE_B200_FP32);
+                if (stream) {
+                    const int nb = static_cast<int>(run_end - i);   // <= span <= kMaxRunBags
+                    if (weighted) pool_run_stream_by_type<true>(p, m, i, nb, b, lane, wsm);
+                    else pool_run_stream_by_type<false>(p, m, i, nb, b, lane, wsm);
+                    done = true;
+                }
             }
+            if (!done) pool_run_general<IdxT, WIDE>(p, m, i, run_end, b, lane, wsm);
         }
         b += run_end - i;
         i = run_end;
@@ -1336,8 +1506,10 @@ __device__ __noinline__ void nobag_position_bytewise(const LookupParams& p, cons
     const int esz = (p.out_ty == TBE_B200_FP32) ? 4 : 2;
     void* seg = static_cast<char*>(p.output) + n * p.out_stride * esz;
     const int64_t idx = static_cast<int64_t>(indices[n]);
-    if (idx < 0) {
-        if (idx < -1 && lane == 0 && p.error_flag) atomicOr(p.error_flag, 1);
+    const bool bad = idx < -1 || idx > 0x7fffffffll;
+    const bool past = !bad && idx >= 0 && static_cast<uint64_t>(idx + 1) * static_cast<uint64_t>(m.stride) > static_cast<uint64_t>(m.avail);
+    if (idx < 0 || bad || past) {
+        if ((bad || past) && lane == 0 && p.error_flag) atomicOr(p.error_flag, bad ? 1 : 4);
         for (int e = lane; e < max(m.D, max_D); e += kWarp) store_scalar(seg, e, 0.0f, p.out_ty);
         return;
     }
@@ -1373,6 +1545,10 @@ __device__ __forceinline__ void nobag_rows(const LookupParams& p, const TableMet
             idx = static_cast<int64_t>(__ldg(indices + n + r0 + g));
             if ((idx < -1 || idx > 0x7fffffffll) && k == 0 && p.error_flag) atomicOr(p.error_flag, 1);
             if (idx > 0x7fffffffll) idx = -1;
+            if (idx >= 0 && static_cast<uint64_t>(idx + 1) * static_cast<uint64_t>(m.stride) > static_cast<uint64_t>(m.avail)) {
+                if (k == 0 && p.error_flag) atomicOr(p.error_flag, 4);
+                idx = -1;
+            }
         }
         const bool ok = idx >= 0;
         const uint8_t* row = m.table + (ok ? idx : 0) * m.stride;
@@ -1516,37 +1692,92 @@ tbe_nobag_kernel(const __grid_constant__ LookupParams p, int64_t num_indices, in
     }
 }
 
-constexpr int kSpanLarge = 16;   // bags per warp when there is plenty of work; a multiple of every group count
+constexpr int kSpanLarge = TBE_SPAN_LARGE;   // bags per warp when there is plenty of work: the more, the fewer bags straddle lane groups
 
-template <typename IdxT, int MINB>
-int launch_pooled(LookupParams p, int max_D, cudaStream_t s)
+// Blocks of a kernel that fit on one SM of the current device (occupancy query, once per device and kernel).
+template <typename Kernel>
+int resident_blocks(Kernel kernel, int variant, int fallback)
 {
-    static int resident = 0;   // blocks that fit on one SM (occupancy query, once)
-    if (resident == 0) {
-        int n = 0;
-        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, tbe_pooled_kernel<IdxT, MINB>, kWarpsPerBlock * kWarp, 0) != cudaSuccess || n <= 0) {
+    constexpr int kMaxDev = 64, kVariants = 4;
+    static std::atomic<int> cached[kMaxDev][kVariants];
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDev) return fallback;
+    int n = cached[dev][variant].load(std::memory_order_relaxed);
+    if (n == 0) {
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, kWarpsPerBlock * kWarp, 0) != cudaSuccess || n <= 0) {
             (void)cudaGetLastError();
-            n = MINB;
+            n = fallback;
         }
-        resident = n;
+        cached[dev][variant].store(n, std::memory_order_relaxed);
     }
-    // Plenty of bags: fixed spans, as many blocks as that takes; the hardware block scheduler evens out the
-    // load.  Otherwise one span per resident warp, rounded up to the number of bags a warp pools side by
-    // side for rows of max_D elements, so that a warp's last step is not a mostly idle one.
+    return n;
+}
+
+// Environment switches, read once: TBE_B200_L2_POLICY (0 = nothing, the default; 2 = access-policy window, see
+// apply_l2_window) and TBE_B200_SPAN (bags per warp, for experiments; 0 = automatic).
+int env_int(const char* name, int dflt)
+{
+    const char* v = getenv(name);
+    return (v && *v) ? atoi(v) : dflt;
+}
+int l2_policy_mode()
+{
+    static const int mode = env_int("TBE_B200_L2_POLICY", 0);
+    return mode;
+}
+
+// TBE_B200_L2_POLICY=2: an access-policy window over dev_weights on the caller's stream, with part of L2 set aside for
+// persisting lines (per-context state that ends with the process).  Off by default: the hot rows of a table are
+// scattered over it (the window cannot single them out, it can only keep a random fraction of the table's lines), and
+// measured no gain.
+void apply_l2_window(const void* base, int64_t bytes, cudaStream_t s)
+{
+    static std::atomic<int> prepared[64];
+    int dev = 0;
+    if (bytes <= 0 || cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return;
+    int max_window = 0, max_persist = 0;
+    cudaDeviceGetAttribute(&max_window, cudaDevAttrMaxAccessPolicyWindowSize, dev);
+    cudaDeviceGetAttribute(&max_persist, cudaDevAttrMaxPersistingL2CacheSize, dev);
+    if (max_window <= 0 || max_persist <= 0) return;
+    if (prepared[dev].exchange(1) == 0) (void)cudaDeviceSetLimit(cudaLimitPersistingL2CacheSize, static_cast<size_t>(max_persist));
+    cudaStreamAttrValue attr{};
+    const size_t win = static_cast<size_t>(bytes < max_window ? bytes : max_window);
+    attr.accessPolicyWindow.base_ptr = const_cast<void*>(base);
+    attr.accessPolicyWindow.num_bytes = win;
+    const float ratio = static_cast<float>(max_persist) / static_cast<float>(win);
+    attr.accessPolicyWindow.hitRatio = ratio < 1.0f ? ratio : 1.0f;
+    attr.accessPolicyWindow.hitProp = cudaAccessPropertyPersisting;
+    attr.accessPolicyWindow.missProp = cudaAccessPropertyStreaming;
+    (void)cudaStreamSetAttribute(s, cudaStreamAttributeAccessPolicyWindow, &attr);
+    (void)cudaGetLastError();
+}
+int forced_span()
+{
+    static const int span = env_int("TBE_B200_SPAN", 0);
+    return span;
+}
+
+template <typename IdxT, bool WIDE>
+int launch_pooled(LookupParams p, cudaStream_t s)
+{
+    const int resident = resident_blocks(tbe_pooled_kernel<IdxT, WIDE>, (sizeof(IdxT) == 8 ? 2 : 0) + (WIDE ? 1 : 0),
+                                         WIDE ? kWideBlocksPerSM : kStreamBlocksPerSM);
+    // Plenty of bags: fixed spans, as many blocks as that takes; the hardware block scheduler evens out the load.
+    // Otherwise the spans are sized so that the warps fill a whole number of waves of resident warps.
     const int64_t slots = static_cast<int64_t>(sm_count()) * resident * kWarpsPerBlock;
-    if (p.num_bags >= slots * kSpanLarge) {
+    const int64_t waves = (p.num_bags + slots * kSpanLarge - 1) / (slots * kSpanLarge);
+    if (waves >= 4) {
         p.span = kSpanLarge;
     } else {
-        int lpr = 2;
-        while (lpr < 32 && lpr * 16 < max_D) lpr <<= 1;
-        const int64_t grain = kWarp / lpr;
-        const int64_t per = (p.num_bags + slots - 1) / slots;
-        p.span = per < grain ? per : grain;
+        const int64_t per = (p.num_bags + slots * waves - 1) / (slots * waves);
+        p.span = per < 1 ? 1 : (per > kSpanLarge ? kSpanLarge : per);
     }
+    const int fs = forced_span();
+    if (fs > 0) p.span = fs > kMaxRunBags ? kMaxRunBags : fs;
     const int64_t warps = (p.num_bags + p.span - 1) / p.span;
     const int64_t blocks = (warps + kWarpsPerBlock - 1) / kWarpsPerBlock;
     if (blocks > 0x7fffffffll) return fail(TBE_B200_ERR_UNSUPPORTED, "lookup: too many bags for one launch");
-    tbe_pooled_kernel<IdxT, MINB><<<static_cast<unsigned>(blocks), kWarpsPerBlock * kWarp, 0, s>>>(p);
+    tbe_pooled_kernel<IdxT, WIDE><<<static_cast<unsigned>(blocks), kWarpsPerBlock * kWarp, 0, s>>>(p);
     return check_launch("tbe_pooled_kernel");
 }
 
@@ -1598,6 +1829,8 @@ extern "C" int tbe_b200_int_nbit_lookup(const tbe_b200_lookup_args* a, tbe_b200_
     p.pooling_mode = a->pooling_mode;
     p.out_ty = a->output_dtype;
     p.row_alignment = a->row_alignment;
+    p.dev_weights_bytes = a->dev_weights_bytes > 0 ? a->dev_weights_bytes : 0;
+    p.idx64 = a->index_bits == 64 ? 1 : 0;
     const int ebits = a->fp8_exponent_bits > 0 ? a->fp8_exponent_bits : 4;
     const int ebias = a->fp8_exponent_bias >= 0 ? a->fp8_exponent_bias : 7;
     p.fp8_shift = static_cast<uint32_t>(16 + ebits);
@@ -1617,6 +1850,9 @@ extern "C" int tbe_b200_int_nbit_lookup(const tbe_b200_lookup_args* a, tbe_b200_
         return check_launch("tbe_nobag_kernel");
     }
     if (p.num_bags == 0) return TBE_B200_OK;
-    return a->index_bits == 32 ? launch_pooled<int32_t, kMinBlocksPerSM>(p, a->max_D, s)
-                               : launch_pooled<int64_t, kMinBlocksPerSM>(p, a->max_D, s);
+    if (l2_policy_mode() == 2) apply_l2_window(a->dev_weights, a->dev_weights_bytes, s);
+    // The widest table decides which build of the kernel runs (max_D is the caller's, like the reference's max_*_D).
+    const bool wide = a->max_D > 512 || (a->max_D & 15) != 0;
+    if (a->index_bits == 32) return wide ? launch_pooled<int32_t, true>(p, s) : launch_pooled<int32_t, false>(p, s);
+    return wide ? launch_pooled<int64_t, true>(p, s) : launch_pooled<int64_t, false>(p, s);
 }

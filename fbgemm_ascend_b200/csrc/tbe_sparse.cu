@@ -43,7 +43,7 @@ __device__ __forceinline__ int64_t block_sum(int64_t v, int64_t* red)
     return t;
 }
 
-// ---- complete cumsum: tile sums, then every tile scans itself behind the sum of the tiles before it ----
+// ---- complete cumsum: tile sums, their running sums (one block), then every tile scans itself behind its carry ----
 
 template <typename T>
 __global__ void __launch_bounds__(kScanThreads) tile_sums_kernel(const T* __restrict__ in, int64_t n, int64_t* __restrict__ tile_sums)
@@ -60,17 +60,55 @@ __global__ void __launch_bounds__(kScanThreads) tile_sums_kernel(const T* __rest
     if (threadIdx.x == 0) tile_sums[blockIdx.x] = s;
 }
 
+// One block turns the tile sums into the sums of everything BEFORE each tile, in place: pieces of 1024 x 4 values, a
+// running carry from piece to piece.  Every tile then reads a single value instead of adding up all the tiles before it.
+constexpr int kCarryThreads = 1024;
+constexpr int kCarryPerThread = 4;
+__global__ void __launch_bounds__(kCarryThreads) exclusive_tile_sums_kernel(int64_t* __restrict__ tile_sums, int64_t tiles)
+{
+    __shared__ int64_t warp_tot[kCarryThreads / 32];
+    __shared__ int64_t piece_total;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    int64_t carry = 0;
+    for (int64_t base = 0; base < tiles; base += kCarryThreads * kCarryPerThread) {
+        const int64_t first = base + static_cast<int64_t>(threadIdx.x) * kCarryPerThread;
+        int64_t v[kCarryPerThread];
+        int64_t mine = 0;
+#pragma unroll
+        for (int j = 0; j < kCarryPerThread; ++j) {
+            v[j] = (first + j < tiles) ? tile_sums[first + j] : 0;
+            mine += v[j];
+        }
+        int64_t incl = mine;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            const int64_t up = __shfl_up_sync(0xffffffffu, incl, d);
+            if (lane >= d) incl += up;
+        }
+        __syncthreads();               // the previous piece's totals have been read
+        if (lane == 31) warp_tot[warp] = incl;
+        __syncthreads();
+        int64_t run = carry + (incl - mine);
+        for (int w = 0; w < warp; ++w) run += warp_tot[w];
+        if (threadIdx.x == kCarryThreads - 1) piece_total = run + mine - carry;
+#pragma unroll
+        for (int j = 0; j < kCarryPerThread; ++j) {
+            if (first + j < tiles) tile_sums[first + j] = run;
+            run += v[j];
+        }
+        __syncthreads();
+        carry += piece_total;
+    }
+}
+
 template <typename T>
-__global__ void __launch_bounds__(kScanThreads) scan_tiles_kernel(const T* __restrict__ in, int64_t n, const int64_t* __restrict__ tile_sums,
+__global__ void __launch_bounds__(kScanThreads) scan_tiles_kernel(const T* __restrict__ in, int64_t n, const int64_t* __restrict__ tiles_before,
                                                                    T* __restrict__ out)
 {
-    __shared__ int64_t red[kScanThreads / 32];
     __shared__ int64_t warp_base[kScanThreads / 32];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    // everything before this tile
-    int64_t before = 0;
-    for (int64_t t = threadIdx.x; t < blockIdx.x; t += kScanThreads) before += tile_sums[t];
-    before = block_sum(before, red);
+    // everything before this tile (a single tile has nothing before it and no scratch)
+    const int64_t before = (gridDim.x > 1) ? tiles_before[blockIdx.x] : 0;
     // thread-contiguous elements: thread i owns [base + 8i, base + 8i + 8)
     const int64_t first = static_cast<int64_t>(blockIdx.x) * kScanTile + static_cast<int64_t>(threadIdx.x) * kScanPerThread;
     int64_t v[kScanPerThread];
@@ -252,11 +290,17 @@ int complete_cumsum_launch(const void* in, int64_t n, int index_bits, void* out,
 {
     const int64_t tiles = (n + kScanTile - 1) / kScanTile;
     if (index_bits == 32) {
-        if (tiles > 1) tile_sums_kernel<int32_t><<<static_cast<unsigned>(tiles), kScanThreads, 0, s>>>(static_cast<const int32_t*>(in), n, tile_sums);
+        if (tiles > 1) {
+            tile_sums_kernel<int32_t><<<static_cast<unsigned>(tiles), kScanThreads, 0, s>>>(static_cast<const int32_t*>(in), n, tile_sums);
+            exclusive_tile_sums_kernel<<<1, kCarryThreads, 0, s>>>(tile_sums, tiles);
+        }
         scan_tiles_kernel<int32_t><<<static_cast<unsigned>(tiles), kScanThreads, 0, s>>>(static_cast<const int32_t*>(in), n, tile_sums,
                                                                                         static_cast<int32_t*>(out));
     } else {
-        if (tiles > 1) tile_sums_kernel<int64_t><<<static_cast<unsigned>(tiles), kScanThreads, 0, s>>>(static_cast<const int64_t*>(in), n, tile_sums);
+        if (tiles > 1) {
+            tile_sums_kernel<int64_t><<<static_cast<unsigned>(tiles), kScanThreads, 0, s>>>(static_cast<const int64_t*>(in), n, tile_sums);
+            exclusive_tile_sums_kernel<<<1, kCarryThreads, 0, s>>>(tile_sums, tiles);
+        }
         scan_tiles_kernel<int64_t><<<static_cast<unsigned>(tiles), kScanThreads, 0, s>>>(static_cast<const int64_t*>(in), n, tile_sums,
                                                                                         static_cast<int64_t*>(out));
     }

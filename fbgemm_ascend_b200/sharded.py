@@ -15,7 +15,8 @@ Two data paths produce identical bytes:
                       blocked permute kernel reading that buffer (no concatenation pass);
 ``exchange="direct"`` one lookup kernel per rank whose epilogue stores every pooled segment straight
                       into the destination rank's output buffer at its final (permuted) column, over
-                      NVLink peer memory; a barrier replaces the exchange and no permute pass is left.
+                      NVLink peer memory; step flags with a bounded device-side wait replace the exchange
+                      and no permute pass is left.
 
 Peer buffers come from ``torch.distributed._symmetric_memory`` (plain peer mappings; no multicast).
 Everything that can be tested without a GPU -- ownership, column maps, permute lists, split sizes --
@@ -161,36 +162,133 @@ class TableWiseShardedLookup:
         return cabi.permute_pooled_embs_blocked(recv, self.offset_dim_list, self.permute_list, self.inv_offset_dim_list, out)
 
     # -- direct peer-store path --------------------------------------------------
+    #: polls (about a microsecond apart) after which a wait for the peers' step flags gives up and records bit 16 in
+    #: ``status``; about two seconds
+    MAX_POLLS = 1 << 21
+
     def _setup_direct(self) -> None:
+        p = self.plan
+        self.status = torch.zeros(1, dtype=torch.int32, device=self.device)   # error word of the lookup and of the waits
+        self._col_offsets = torch.tensor(p.local_final_cols(), dtype=torch.int64, device=self.device)
+        self._step = 0
+        if p.world == 1:
+            # one rank: the "exchange" is the column remap alone; plain local buffers, nothing to wait for
+            self._out2 = torch.empty((2, p.local_batch, p.total_D), dtype=self.out_dtype, device=self.device)
+            self._dest_ptrs = [None, None]
+            return
         import torch.distributed._symmetric_memory as symm_mem
 
-        p = self.plan
+        gname = self.group.group_name if self.group is not None else dist.group.WORLD.group_name
         # one output buffer per rank, mapped into every peer; double-buffered so a rank may start writing
         # step n+1 while a slow peer still reads step n
         self._symm = symm_mem.empty((2, p.local_batch, p.total_D), dtype=self.out_dtype, device=self.device)
-        self._hdl = symm_mem.rendezvous(self._symm, self.group.group_name if self.group is not None else dist.group.WORLD.group_name)
+        self._hdl = symm_mem.rendezvous(self._symm, gname)
+        self._out2 = self._symm
         ptrs = [int(x) for x in self._hdl.buffer_ptrs]
         half = p.local_batch * p.total_D * self._symm.element_size()
         self._dest_ptrs = [torch.tensor([q + k * half for q in ptrs], dtype=torch.int64, device=self.device) for k in range(2)]
-        self._col_offsets = torch.tensor(p.local_final_cols(), dtype=torch.int64, device=self.device)
-        self._step = 0
+        # step flags: flags[k][r] on rank s = the last step of buffer k that rank r has finished storing into rank s
+        self._flags = symm_mem.empty((2, p.world), dtype=torch.int64, device=self.device)
+        self._flags.zero_()
+        self._fhdl = symm_mem.rendezvous(self._flags, gname)
+        fptrs = [int(x) for x in self._fhdl.buffer_ptrs]
+        self._flag_ptrs = [torch.tensor([q + k * p.world * 8 for q in fptrs], dtype=torch.int64, device=self.device) for k in range(2)]
+        torch.cuda.synchronize(self.device)
+        dist.barrier(group=self.group)        # every rank's flags are zero before anyone raises one
 
     def forward_direct(self, indices, offsets, weights=None) -> torch.Tensor:
         from . import cabi
         p, tb = self.plan, self.tables
         k = self._step & 1
         self._step += 1
-        out = self._symm[k]
+        out = self._out2[k]
         cabi.lookup(tb.weights_dev, tb.weights_offsets, tb.weights_tys, tb.D_offsets, tb.total_D, tb.max_D, indices, offsets,
                     int(tb.pooling_mode), out, indice_weights=weights, row_alignment=tb.row_alignment,
                     output_stride=p.total_D, output_col_offsets=self._col_offsets, dest_outputs=self._dest_ptrs[k],
-                    rows_per_dest=p.local_batch, B=p.global_batch)
-        # every rank's stores into this rank's buffer are complete once all ranks passed this point
-        self._hdl.barrier(channel=k)
+                    rows_per_dest=p.local_batch if p.world > 1 else 0, B=p.global_batch, error_flag=self.status)
+        if p.world > 1:
+            # this rank's stores into every peer are in place -> raise its flag there; then wait (bounded) until
+            # every peer has raised its flag here: the buffer then holds the whole step
+            value = (self._step + 1) // 2
+            cabi.signal_peers(self._flag_ptrs[k], p.world, p.rank, value)
+            cabi.wait_flags(self._flags[k], p.world, value, self.MAX_POLLS, self.status)
         return out
+
+    def check_status(self) -> int:
+        """Reads the error word (a device-to-host copy): 0, or the bits of ``tbe_b200_lookup_args.error_flag`` and bit 16
+        (a peer's step flag did not arrive in time)."""
+        return int(self.status.item())
 
     def forward(self, indices, offsets, weights=None) -> torch.Tensor:
         return self.forward_direct(indices, offsets, weights) if self.exchange == "direct" else \
             self.forward_nccl(indices, offsets, weights)
 
     __call__ = forward
+
+
+class FeatureMajorInputDist:
+    """Turns the feature-major request every rank holds for ITS samples into the table-major request over the
+    GLOBAL batch that the rank's lookup needs (the step in front of the sharded lookup).
+
+    Rank ``s`` starts with ``lengths [T_global, B_local]`` and the matching ``indices`` (all tables, its own
+    ``B_local = B_global / world`` samples).  Per call:
+
+      1. ``permute_2D_sparse_data`` groups the tables by owning rank (the order of ``ShardPlan.exchanged_order``);
+      2. the lengths go through an all-to-all with equal splits, the send / receive counts of the indices are
+         summed on the device and read by the host once (the collective needs them as host integers -- the
+         reference reads its output size the same way, permute2d_sparse_data.cpp:100-108), then the indices (and
+         per-sample weights) go through an all-to-all with those splits into local memory;
+      3. what arrived is ordered (source rank, local table, sample); a second ``permute_2D_sparse_data`` over the
+         ``world * T_local`` segments puts it into (local table, source rank, sample) order, which is table-major
+         over the global batch, and ``asynchronous_complete_cumsum`` turns the lengths into offsets.
+
+    The three operators are the package's own (``torch.ops.fbgemm.*``) unless replaced through the hooks, which
+    lets the plumbing run on CPU ranks (gloo) in the tests.
+    """
+
+    def __init__(self, plan: ShardPlan, group=None, device: Optional[torch.device] = None,
+                 permute_fn: Optional[Callable] = None, cumsum_fn: Optional[Callable] = None,
+                 index_dtype: torch.dtype = torch.int64) -> None:
+        self.plan = plan
+        self.group = group
+        self.device = device if device is not None else torch.device("cpu")
+        self.index_dtype = index_dtype
+        self.permute_fn = permute_fn or (lambda perm, lengths, values, weights, total:
+                                         torch.ops.fbgemm.permute_2D_sparse_data(perm, lengths, values, weights, total))
+        self.cumsum_fn = cumsum_fn or (lambda x: torch.ops.fbgemm.asynchronous_complete_cumsum(x))
+        p = plan
+        self.T_loc = len(p.local_tables)
+        if any(len(p.tables_of(r)) != self.T_loc for r in range(p.world)):
+            raise ValueError("every rank must own the same number of tables")
+        t32 = lambda v: torch.tensor(v, dtype=torch.int32, device=self.device)
+        self.by_owner = t32(p.exchanged_order)                                            # step 1
+        self.to_table_major = t32([s * self.T_loc + j for j in range(self.T_loc) for s in range(p.world)])   # step 3
+
+    def __call__(self, lengths: torch.Tensor, indices: torch.Tensor, weights: Optional[torch.Tensor] = None):
+        p, w, T_loc, B_loc = self.plan, self.plan.world, self.T_loc, self.plan.local_batch
+        if tuple(lengths.shape) != (len(p.dims), B_loc):
+            raise ValueError(f"lengths must be [{len(p.dims)}, {B_loc}], got {tuple(lengths.shape)}")
+        # 1. tables grouped by owner: owner r's tables are rows [r * T_loc, (r + 1) * T_loc) of the result
+        len_by_owner, idx_by_owner, w_by_owner = self.permute_fn(self.by_owner, lengths, indices, weights, indices.numel())
+        # 2. exchange
+        send_counts = len_by_owner.view(w, -1).sum(1, dtype=torch.int64)
+        if w == 1:
+            len_recv, idx_recv, w_recv = len_by_owner, idx_by_owner, w_by_owner
+            total = idx_by_owner.numel()
+        else:
+            len_recv = torch.empty_like(len_by_owner)
+            dist.all_to_all_single(len_recv.view(-1), len_by_owner.contiguous().view(-1), group=self.group)
+            recv_counts = len_recv.view(w, -1).sum(1, dtype=torch.int64)
+            counts = torch.stack([send_counts, recv_counts]).cpu()                        # the one host read of the step
+            send_l, recv_l = counts[0].tolist(), counts[1].tolist()
+            total = int(sum(recv_l))
+            idx_recv = torch.empty(total, dtype=indices.dtype, device=indices.device)
+            dist.all_to_all_single(idx_recv, idx_by_owner.contiguous(), recv_l, send_l, group=self.group)
+            w_recv = None
+            if weights is not None:
+                w_recv = torch.empty(total, dtype=weights.dtype, device=weights.device)
+                dist.all_to_all_single(w_recv, w_by_owner.contiguous(), recv_l, send_l, group=self.group)
+        # 3. (source rank, local table, sample) -> (local table, source rank, sample) = table-major over the global batch
+        len_tm, idx_tm, w_tm = self.permute_fn(self.to_table_major, len_recv.view(w * T_loc, B_loc), idx_recv, w_recv, total)
+        offsets = self.cumsum_fn(len_tm.reshape(-1)).to(self.index_dtype)
+        return idx_tm.to(self.index_dtype), offsets, w_tm

@@ -77,19 +77,27 @@ def table_bytes(ws: WorkloadSpec, row_alignment: int = 16) -> int:
 
 
 def build_tables(ws: WorkloadSpec, device: torch.device, table_seed_offset: int = 0,
-                 chunk_rows: int = 1 << 20) -> IntNBitTableBatchedEmbeddingBags:
+                 chunk_rows: int = 1 << 20, row_hook: Optional[Callable] = None) -> IntNBitTableBatchedEmbeddingBags:
     """Generate fp32 rows on the device chunk by chunk, quantize them into the flat table buffer
-    and drop the fp32 (so a 110 GB shard never needs a second copy)."""
+    and drop the fp32 (so a 110 GB shard never needs a second copy).  ``row_hook(t, r0, x)`` sees every
+    fp32 chunk (rows r0.. of table t) before it is dropped, e.g. to keep a sample of source rows."""
     specs = [(f"t{t}", ws.E, ws.dims[t], ws.tys[t]) for t in range(ws.T)]
     m = IntNBitTableBatchedEmbeddingBags(specs, device=device, pooling_mode=ws.pooling, output_dtype=ws.output_dtype,
                                          indices_dtype=ws.index_dtype)
     kind, val = ws.table_dist.split(":")
     val = float(val)
 
+    row0 = {}
+
     def make_rows(t, n, D, gen):
         if kind == "normal":
-            return torch.randn(n, D, device=device, generator=gen) * val
-        return (torch.rand(n, D, device=device, generator=gen) * 2.0 - 1.0) * val
+            x = torch.randn(n, D, device=device, generator=gen) * val
+        else:
+            x = (torch.rand(n, D, device=device, generator=gen) * 2.0 - 1.0) * val
+        if row_hook is not None:
+            row_hook(t, row0.get(t, 0), x)
+            row0[t] = row0.get(t, 0) + n
+        return x
 
     m.fill_random_weights(make_rows, seed=ws.seed * 1000 + table_seed_offset, chunk_rows=chunk_rows)
     return m

@@ -13,7 +13,8 @@
  *     comment says "host".  The library never allocates, frees or synchronises.
  *   - Every call returns TBE_B200_OK (0) or a negative tbe_b200_status; the
  *     message of the last failure on the calling thread is tbe_b200_last_error().
- *   - Calls are re-entrant and may be issued from any thread.
+ *   - Calls are re-entrant and may be issued from any thread (the only state kept between calls is a
+ *     per-device cache of device properties, updated atomically).
  *   - `stream` is a cudaStream_t (0 = the default stream).
  */
 #ifndef TBE_B200_H_
@@ -79,7 +80,8 @@ typedef enum { TBE_B200_POOL_SUM = 0, TBE_B200_POOL_MEAN = 1, TBE_B200_POOL_NONE
  */
 typedef struct {
     const uint8_t* dev_weights;         /* all tables, flat bytes */
-    int64_t dev_weights_bytes;          /* size of dev_weights (checked against nothing on device; 0 = unknown) */
+    int64_t dev_weights_bytes;          /* size of dev_weights; 0 = unknown.  When known, a row that would end past
+                                           its table (the next table's start, or the end of dev_weights) is skipped */
     const int64_t* weights_offsets;     /* [T] byte offset of each table */
     const uint8_t* weights_tys;         /* [T] tbe_b200_sparse_type per table */
     const int32_t* D_offsets;           /* [T+1] prefix sum of the tables' D */
@@ -102,10 +104,13 @@ typedef struct {
     const int64_t* output_col_offsets;  /* [T] or NULL (pooled modes) */
     void* const* dest_outputs;          /* [ceil(B / rows_per_dest)] device array of base pointers, or NULL */
     int64_t rows_per_dest;              /* used only with dest_outputs */
-    int32_t* error_flag;                /* optional device word: or'ed with 1 when an index outside [-1, 2^31) is
-                                           met (that row is skipped), with 2 when a warp gave up waiting for rows
-                                           it had requested (its remaining bags are left unwritten; the wait is
-                                           bounded so that the kernel always ends); NULL = no reporting */
+    int32_t* error_flag;                /* optional device word, or'ed with
+                                             1  an index outside [-1, 2^31) was met (that row is skipped),
+                                             4  an index at or past the end of its table was met (dev_weights_bytes
+                                                known; the row is skipped like -1 and never read),
+                                             8  offsets[T*B] != num_indices, or offsets that point outside
+                                                `indices` (those bags are not read);
+                                           NULL = no reporting (the checks that skip rows are made all the same) */
 } tbe_b200_lookup_args;
 
 /* Pooled (SUM / MEAN) or sequence (NONE) lookup over fused INT8 / INT4 / INT2 /
@@ -228,6 +233,23 @@ int tbe_b200_permute_2d_sparse_copy(const int32_t* permute, int64_t T_out, int64
                                     int64_t value_bytes, const void* weights, int64_t weight_row_bytes, void* out_values,
                                     void* out_weights, int64_t out_capacity, const void* scratch,
                                     tbe_b200_stream_t stream);
+
+/* ---- step flags of a table-wise sharded lookup (one process per GPU) ---------------------------- */
+
+/* A rank tells its peers that the pooled rows it stored into their output buffers for step `value` are in place:
+ * it writes `value` to peer_flags[r][my_rank] for every rank r (its own included).  peer_flags is a DEVICE array of
+ * `world` pointers, each to a peer-mapped array of `world` int64 flags in rank r's memory.  Enqueue it on the stream
+ * of the lookup, after the lookup: the flag is ordered after everything the GPU wrote before this call (release at
+ * system scope).  Plain peer stores; no multicast.  The reference has no multi-device code and no counterpart. */
+int tbe_b200_signal_peers(int64_t* const* peer_flags, int32_t world, int32_t my_rank, int64_t value,
+                          tbe_b200_stream_t stream);
+
+/* Waits on the device until flags[r] >= value for every r < world (flags: this rank's own array, written by the
+ * peers' tbe_b200_signal_peers).  The wait is bounded: a flag that is not up after max_polls polls (about a
+ * microsecond apart) sets bit 16 of *error_flag (if given) and the kernel returns, so the stream always drains;
+ * the caller reads the word to learn that a peer is late or gone.  No counterpart in the reference. */
+int tbe_b200_wait_flags(const int64_t* flags, int32_t world, int64_t value, int64_t max_polls, int32_t* error_flag,
+                        tbe_b200_stream_t stream);
 
 /* Message of the last failure on the calling thread ("" if none).  Host pointer,
  * valid until the next failing call on the same thread. */

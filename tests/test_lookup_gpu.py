@@ -217,3 +217,99 @@ def test_scatter_to_destinations_with_column_remap():
                 rows_per_dest=8)
     got = torch.cat(parts, 0).float().cpu().numpy()
     assert_close(got, want_perm, O.FP16, "scatter+remap")
+
+
+@pytest.mark.parametrize("weights_ty,D", [(O.INT8, 128), (O.INT4, 64), (O.FP16, 32), (O.INT8, 20)])
+@pytest.mark.parametrize("pooling", [O.SUM, O.NONE])
+def test_row_past_the_table_is_skipped_and_reported(weights_ty, D, pooling):
+    """An index >= the table's row count is never dereferenced: with dev_weights_bytes known the row is
+    treated like a pruned one (-1) and bit 4 of the error word is set.  Checked for a table in the
+    middle of dev_weights (the row would belong to the next table) and for the last one (the row would
+    lie outside the buffer)."""
+    import torch
+    from fbgemm_ascend_b200 import cabi
+
+    rng = np.random.default_rng(11)
+    E = [40, 30, 50]
+    c = make_case(rng, [weights_ty] * 3, [D] * 3, E, 8, np.concatenate([np.full(8, 9), np.full(8, 12), np.full(8, 5)]), np.int64)
+    offs = c.offsets
+    bad_positions = [int(offs[8]) + 3, int(offs[16]) + 1, int(offs[23]) + 2]   # one in the middle table, two in the last
+    for q in bad_positions:
+        t = int(np.searchsorted(offs[::8], q, side="right") - 1)
+        c.indices[q] = E[t] + (0 if q == bad_positions[0] else 1000)
+    d = torch.device("cuda")
+    t_ = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(d)
+    flag = torch.zeros(1, dtype=torch.int32, device=d)
+    n_out = c.indices.size if pooling == O.NONE else 8
+    width = D if pooling == O.NONE else 3 * D
+    out = torch.full((n_out, width), 3.0, dtype=torch.float32, device=d)
+    cabi.lookup(t_(c.dev_weights), t_(c.weights_offsets), t_(c.weights_tys), t_(c.D_offsets), 3 * D, D, t_(c.indices),
+                t_(c.offsets), pooling, out, error_flag=flag)
+    assert int(flag.item()) == 4
+    for q in bad_positions:
+        c.indices[q] = -1
+    assert_close(out.cpu().numpy(), oracle_lookup(c, pooling, O.FP32), O.FP32, "rows past the table pruned")
+
+
+def test_offsets_that_disagree_with_the_index_count_are_reported():
+    """offsets[T*B] != indices.numel() (the reference kernel asserts on it) sets bit 8; positions past
+    `indices` are never read."""
+    import torch
+    from fbgemm_ascend_b200 import cabi
+
+    rng = np.random.default_rng(12)
+    c = make_case(rng, [O.INT8, O.INT8], [64, 64], [100, 100], 8, 6, np.int32)
+    d = torch.device("cuda")
+    t_ = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(d)
+    flag = torch.zeros(1, dtype=torch.int32, device=d)
+    out = torch.zeros((8, 128), dtype=torch.float16, device=d)
+    short = c.indices[:-5]                      # offsets describe 5 more positions than there are indices
+    cabi.lookup(t_(c.dev_weights), t_(c.weights_offsets), t_(c.weights_tys), t_(c.D_offsets), 128, 64, t_(short), t_(c.offsets),
+                O.SUM, out, error_flag=flag)
+    assert int(flag.item()) & 8
+    flag.zero_()
+    cabi.lookup(t_(c.dev_weights), t_(c.weights_offsets), t_(c.weights_tys), t_(c.D_offsets), 128, 64, t_(c.indices), t_(c.offsets),
+                O.SUM, out, error_flag=flag)
+    assert int(flag.item()) == 0
+    assert_close(out.float().cpu().numpy(), oracle_lookup(c, O.SUM, O.FP16), O.FP16, "consistent offsets")
+
+
+@pytest.mark.parametrize("out_dtype", ["float16", "float32"])
+def test_scatter_with_rows_that_are_not_16_byte_aligned(out_dtype):
+    """Destination scatter with an output row of 68 elements (136 or 272 bytes: alternate rows are
+    misaligned for 16-byte stores), a batch that is not a multiple of the lane-group count, and bag lengths
+    that differ a lot, so that bags straddle the lane groups' ranges."""
+    import torch
+    from fbgemm_ascend_b200 import cabi
+
+    rng = np.random.default_rng(13)
+    dims = [32, 16, 20]
+    B = 13
+    lens = rng.integers(0, 60, 3 * B)
+    lens[5] = 300
+    c = make_case(rng, [O.INT8, O.INT8, O.INT8], dims, [200] * 3, B, lens, np.int32)
+    out_ty = O.FP16 if out_dtype == "float16" else O.FP32
+    want = oracle_lookup(c, O.SUM, out_ty)
+    d = torch.device("cuda")
+    t_ = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(d)
+    rows_per_dest = 5
+    parts = [torch.zeros((rows_per_dest, 68), dtype=getattr(torch, out_dtype), device=d) for _ in range(3)]
+    ptrs = torch.tensor([p.data_ptr() for p in parts], dtype=torch.int64, device=d)
+    cabi.lookup(t_(c.dev_weights), t_(c.weights_offsets), t_(c.weights_tys), t_(c.D_offsets), 68, 32, t_(c.indices),
+                t_(c.offsets), O.SUM, parts[0], dest_outputs=ptrs, rows_per_dest=rows_per_dest, output_stride=68)
+    got = torch.cat(parts, 0)[:B].float().cpu().numpy()
+    assert_close(got, want, out_ty, "misaligned scatter")
+
+
+@pytest.mark.parametrize("weights_ty", [O.INT8, O.INT4, O.FP16, O.FP8, O.FP32])
+@pytest.mark.parametrize("D", [64, 128, 256, 512])
+@pytest.mark.parametrize("weighted", [False, True])
+def test_bags_that_straddle_lane_group_ranges(weights_ty, D, weighted):
+    """Few, very unequal bags per table: one bag of a thousand rows next to empty and tiny ones, so that a
+    bag is summed in pieces by several lane groups and put together by its owner; also a table whose bags
+    are all empty and a batch of a single bag."""
+    rng = np.random.default_rng(seed_of(weights_ty, D, weighted))
+    for B, lens in ((5, [0, 1000, 0, 3, 1, 0, 0, 0, 0, 0, 2, 0, 0, 777, 1]), (1, [613, 0, 5]), (3, [1, 1, 1, 0, 0, 0, 64, 64, 65])):
+        c = make_case(rng, [weights_ty] * 3, [D] * 3, [300, 50, 1000], B, np.asarray(lens), np.int64, weighted, prune_frac=0.01)
+        for pooling, out_ty in ((O.SUM, O.FP16), (O.MEAN, O.FP32)):
+            run(c, pooling, out_ty, f"straddle B={B}")

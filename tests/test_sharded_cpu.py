@@ -126,3 +126,87 @@ def test_rank_failure_before_exchange_surfaces_on_peer():
     res = _run(2, fail=True)
     assert res[1][1] is False and "injected failure" in res[1][2]
     assert res[0][1] is False and res[0][2] != ""
+
+
+def _local_request(c, rank, world):
+    """The feature-major request rank `rank` holds: every table's bags for its own B/world samples."""
+    T, B = c.T, c.B
+    Bl = B // world
+    lens = np.diff(c.offsets).reshape(T, B)
+    l_loc = lens[:, rank * Bl:(rank + 1) * Bl]
+    idx = np.concatenate([c.indices[c.offsets[t * B + rank * Bl]:c.offsets[t * B + (rank + 1) * Bl]] for t in range(T)])
+    return np.ascontiguousarray(l_loc), idx
+
+
+def _dist_main(rank, world, port, weighted, q):
+    try:
+        os.environ["MASTER_ADDR"] = "127.0.0.1"
+        os.environ["MASTER_PORT"] = str(port)
+        import datetime
+        dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=20))
+        from fbgemm_ascend_b200.sharded import FeatureMajorInputDist, ShardPlan
+        c, dims, tys, order = _global_case()
+        B = c.B
+        plan = ShardPlan(world=world, rank=rank, dims=dims, feature_order=order, global_batch=B)
+
+        def permute_fn(perm, lengths, values, weights, total):
+            l, v, w = O.permute_2d_sparse_data(perm.numpy(), lengths.numpy(), values.numpy(), None if weights is None else weights.numpy())
+            assert v.size == total
+            return torch.from_numpy(l), torch.from_numpy(v), None if w is None else torch.from_numpy(w)
+
+        ind = FeatureMajorInputDist(plan, group=None, device=torch.device("cpu"), permute_fn=permute_fn,
+                                    cumsum_fn=lambda x: torch.from_numpy(O.complete_cumsum(x.numpy())))
+        l_loc, idx_loc = _local_request(c, rank, world)
+        wts = None
+        if weighted:
+            wts = torch.from_numpy(idx_loc.astype(np.float32) * 0.5 + rank)      # a weight that names its index and its source
+        idx_tm, offs_tm, w_tm = ind(torch.from_numpy(l_loc), torch.from_numpy(idx_loc), wts)
+        # expected: the global batch's bags of this rank's tables, table-major
+        offs = c.offsets
+        want_idx = np.concatenate([c.indices[offs[t * B]:offs[(t + 1) * B]] for t in plan.local_tables])
+        want_len = np.concatenate([np.diff(offs[t * B:(t + 1) * B + 1]) for t in plan.local_tables])
+        want_off = np.concatenate([[0], np.cumsum(want_len)])
+        ok = np.array_equal(idx_tm.numpy(), want_idx) and np.array_equal(offs_tm.numpy(), want_off)
+        if weighted:
+            Bl = B // world
+            src = np.concatenate([np.repeat(np.arange(B) // Bl, np.diff(offs[t * B:(t + 1) * B + 1])) for t in plan.local_tables])
+            ok = ok and np.array_equal(w_tm.numpy(), want_idx.astype(np.float32) * 0.5 + src)
+        q.put((rank, bool(ok), ""))
+        dist.destroy_process_group()
+    except Exception as e:
+        q.put((rank, False, f"{type(e).__name__}: {e}\n{traceback.format_exc()[-800:]}"))
+
+
+@pytest.mark.parametrize("weighted", [False, True])
+def test_feature_major_input_dist_two_ranks(weighted):
+    """Index all-to-all in front of the lookup: two CPU ranks, each with the feature-major request of its own
+    samples, end up with the table-major request of the global batch for their own tables."""
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_dist_main, args=(r, 2, port, weighted, q)) for r in range(2)]
+    for pr in procs:
+        pr.start()
+    res = sorted(q.get(timeout=120) for _ in range(2))
+    for pr in procs:
+        pr.join(timeout=60)
+        if pr.is_alive():
+            pr.kill()
+    assert all(ok for _, ok, _ in res), res
+
+
+def test_feature_major_input_dist_one_rank():
+    """world = 1: no exchange; the feature-major request is already table-major, offsets are the running sums."""
+    from fbgemm_ascend_b200.sharded import FeatureMajorInputDist, ShardPlan
+    c, dims, tys, order = _global_case()
+    plan = ShardPlan(world=1, rank=0, dims=dims, feature_order=order, global_batch=c.B)
+
+    def permute_fn(perm, lengths, values, weights, total):
+        l, v, w = O.permute_2d_sparse_data(perm.numpy(), lengths.numpy(), values.numpy(), None)
+        return torch.from_numpy(l), torch.from_numpy(v), None
+
+    ind = FeatureMajorInputDist(plan, device=torch.device("cpu"), permute_fn=permute_fn,
+                                cumsum_fn=lambda x: torch.from_numpy(O.complete_cumsum(x.numpy())))
+    l_loc, idx_loc = _local_request(c, 0, 1)
+    idx_tm, offs_tm, _ = ind(torch.from_numpy(l_loc), torch.from_numpy(idx_loc))
+    assert np.array_equal(idx_tm.numpy(), c.indices) and np.array_equal(offs_tm.numpy(), c.offsets)

@@ -43,6 +43,13 @@ def _rank_main(rank, world, port, q):
         tables = W.build_tables(ws, dev, table_seed_offset=rank)
         batch = W.make_batch(ws, dev, batch_seed=0, table_ids=plan.local_tables)
         pooled = tables.forward(batch.indices, batch.offsets, None)           # [B, 6*128] local tables, global batch
+        # this rank's pooled rows against the CPU oracle (the rest of the chain below is bit-exact copying)
+        import oracle as O
+        cpu = O.tbe_lookup(tables.weights_dev.cpu().numpy(), tables.weights_offsets.cpu().numpy(), tables.weights_tys.cpu().numpy(),
+                           tables.D_offsets.cpu().numpy(), batch.indices.cpu().numpy(), batch.offsets.cpu().numpy(), O.SUM, None,
+                           O.FP16, impl="ref").astype(np.float32)
+        err = np.abs(pooled.float().cpu().numpy() - cpu)
+        oracle_ok = bool(np.all(err <= 1e-3 + 1e-3 * np.abs(cpu)))
         # reference: gather every rank's pooled block, order the tables by global id, permute with the operator
         gathered = [torch.empty_like(pooled) for _ in range(world)]
         dist.all_gather(gathered, pooled)
@@ -60,6 +67,24 @@ def _rank_main(rank, world, port, q):
                 got = sh(batch.indices, batch.offsets, None)
             torch.cuda.synchronize()
             ok[mode] = bool(torch.equal(got, want))
+            if mode == "direct":
+                ok["status"] = sh.check_status()
+        ok["oracle"] = oracle_ok
+        # the index all-to-all in front of the lookup: from every rank's feature-major request for its own samples to
+        # this rank's table-major request for the global batch -- must reproduce the pre-placed batch bit for bit
+        from fbgemm_ascend_b200.sharded import FeatureMajorInputDist
+        Bl, B = plan.local_batch, ws.B
+        per_rank = [W.make_batch(ws, dev, batch_seed=0, table_ids=plan.tables_of(r)) for r in range(world)]
+        lens_fm, idx_fm = [], []
+        for t in range(T_glob):
+            br = per_rank[t % world]
+            j = t // world
+            o = br.offsets[j * B + rank * Bl: j * B + (rank + 1) * Bl + 1]
+            lens_fm.append(o[1:] - o[:-1])
+            idx_fm.append(br.indices[int(o[0]):int(o[-1])])
+        ind = FeatureMajorInputDist(plan, group=dist.group.WORLD, device=dev)
+        idx_tm, offs_tm, _ = ind(torch.stack(lens_fm), torch.cat(idx_fm))
+        ok["input_dist"] = bool(torch.equal(idx_tm, batch.indices) and torch.equal(offs_tm, batch.offsets))
         q.put((rank, ok, ""))
         dist.barrier()
         dist.destroy_process_group()
@@ -85,7 +110,7 @@ def _run(world):
 def test_world_one_both_paths():
     res = _run(1)
     assert res[0][2] == "", res[0][2]
-    assert res[0][1] == {"nccl": True, "direct": True}, res
+    assert res[0][1] == {"nccl": True, "direct": True, "status": 0, "oracle": True, "input_dist": True}, res
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
@@ -93,4 +118,35 @@ def test_two_ranks_both_paths_bit_exact():
     res = _run(2)
     for rank, ok, err in res:
         assert err == "", err
-        assert ok == {"nccl": True, "direct": True}, res
+        assert ok == {"nccl": True, "direct": True, "status": 0, "oracle": True, "input_dist": True}, res
+
+
+def test_wait_for_step_flags_is_bounded():
+    """The device-side wait for the peers' step flags gives up after max_polls polls: a flag that nobody raises makes
+    the wait run out, bit 16 appears in the error word, the kernel returns and the stream stays usable.  (The failure is
+    made on the host side -- a flag that is simply never written -- not by faulting anything.)"""
+    from fbgemm_ascend_b200 import cabi
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    world = 4
+    flags = torch.zeros(world, dtype=torch.int64, device=dev)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    ptrs = torch.tensor([flags.data_ptr()] * world, dtype=torch.int64, device=dev)
+    # three of four "ranks" raise their flag for step 1 (all four arrays are this one array here); rank 2 never does
+    for r in (0, 1, 3):
+        cabi.signal_peers(ptrs, world, r, 1)
+    cabi.wait_flags(flags, world, 1, 2000, status)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 16
+    assert flags.tolist() == [1, 1, 0, 1]
+    # once the last flag is up the same wait passes, and later steps need later values
+    status.zero_()
+    cabi.signal_peers(ptrs, world, 2, 1)
+    cabi.wait_flags(flags, world, 1, 2000, status)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    cabi.wait_flags(flags, world, 2, 500, status)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 16
+    with pytest.raises(RuntimeError, match="max_polls"):
+        cabi.wait_flags(flags, world, 1, 0, status)
