@@ -825,22 +825,24 @@ __device__ __forceinline__ unsigned short accum_header(uint32_t hdr, float w, fl
 template <int TY, bool WEIGHTED, bool FOLD, int NW>
 __device__ __forceinline__ void accum_codes(const uint32_t (&words)[NW], unsigned short scale_h, float ws, float* acc)
 {
-    if constexpr (TY == TBE_B200_INT8) {
+    if constexpr (TY == TBE_B200_INT8 && FOLD) {
+        // One byte permute per code builds the register the mixed FMA wants: its two fp16 operands side by side,
+        // (1024 + q) below (bytes q, 0x64) and the row scale above.  With the operands in two registers the compiler
+        // spends a move per FMA to bring them together (measured: 16 moves for 16 FMAs, none in this form).
+        const uint32_t y = (static_cast<uint32_t>(scale_h) << 16) | 0x6400u;
+#pragma unroll
+        for (int i = 0; i < NW; ++i) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const uint32_t x = __byte_perm(words[i], y, 0x7650u | j);
+                asm("{ .reg .b16 l, h; mov.b32 {l, h}, %1; fma.rn.f32.f16 %0, l, h, %0; }" : "+f"(acc[4 * i + j]) : "r"(x));
+            }
+        }
+    } else if constexpr (TY == TBE_B200_INT8) {
 #pragma unroll
         for (int i = 0; i < NW; ++i) {
             const uint32_t c = words[i];
             // bytes 0 and 2, then bytes 1 and 3, placed in the mantissas of half2(1024, 1024)
-#ifdef TBE_SPLAT_DECODE
-            if constexpr (FOLD) {
-                // one code per register: bytes (q, 0x64, 0, 0) = the half 1024 + q in the low 16 bits
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const uint32_t x = __byte_perm(c, 0x6400u, 0x4450u | j);
-                    asm("fma.rn.f32.f16 %0, %1, %2, %0;" : "+f"(acc[4 * i + j]) : "h"(static_cast<unsigned short>(x)), "h"(scale_h));
-                }
-                continue;
-            }
-#endif
             uint32_t even = (c & 0x00FF00FFu) | 0x64006400u;
             uint32_t odd = __byte_perm(c, 0x64646464u, 0x4341);
             if constexpr (!FOLD) {
@@ -1306,12 +1308,14 @@ __device__ __forceinline__ void pool_run_stream_by_width(const LookupParams& p, 
 }
 
 #ifdef TBE_STREAM_BENCH_SHAPES_ONLY
-// Experiment builds: only the INT8 D <= 128 unweighted 16-bit-output stream is compiled; everything else must not be run.
+// Experiment builds: only the unweighted INT8 D = 128 16-bit-output stream and the unweighted INT4 streams are compiled;
+// everything else must not be run.
 template <bool WEIGHTED>
 __device__ __forceinline__ void pool_run_stream_by_type(const LookupParams& p, const TableMeta& m, int64_t i0, int nb, int64_t b,
                                                         int lane, uint32_t wsm)
 {
     if constexpr (!WEIGHTED) {
+        if (m.ty == TBE_B200_INT4) pool_run_stream_by_width<TBE_B200_INT4, false, false>(p, m, i0, nb, b, lane, wsm);
         if (m.ty == TBE_B200_INT8 && p.out_ty != TBE_B200_FP32 && m.D == 128) {
 #ifdef TBE_BENCH_EPL16
             pool_run_stream<TBE_B200_INT8, 8, 16, false, true>(p, m, i0, nb, b, lane, wsm);
