@@ -406,6 +406,56 @@ def measure_plain(name, args, sampler, steps, index_dtype=None, scale_e=1.0, sca
     return res, (tables, batches, ws)
 
 
+def second_tier_kernels() -> dict:
+    """The other kernels of the path (quantizers, pooled permute, cumsum, sparse-data permute, sequence lookup), each
+    timed alone with CUDA events on inputs larger than L2: microseconds, achieved GB/s of input + output bytes, and
+    the fraction of the measured copy bandwidth."""
+    import torch
+    peak, _ = _peaks()
+    dev = torch.device("cuda", torch.cuda.current_device())
+    res = {}
+
+    def timeit(fn, reps=5, inner=4):
+        for _ in range(2):
+            fn()
+        ts = []
+        for _ in range(reps):
+            ts.append(timed(lambda i: fn(), inner) / inner)
+        return statistics.median(ts)
+
+    def rec(name, ms, nbytes):
+        res[name] = {"us": round(ms * 1e3, 1), "gbs": round(nbytes / ms / 1e6), "frac": round(nbytes / ms / 1e6 / peak, 3)}
+
+    ops = torch.ops.fbgemm
+    N, D = 1 << 20, 128
+    x = torch.randn(N, D, device=dev) * 0.05
+    q = ops.FloatToFused8BitRowwiseQuantized(x)
+    rec("FloatToFused8BitRowwiseQuantized 1Mx128", timeit(lambda: ops.FloatToFused8BitRowwiseQuantized(x)), N * (5 * D + 8))
+    rec("Fused8BitRowwiseQuantizedToFloat 1Mx128", timeit(lambda: ops.Fused8BitRowwiseQuantizedToFloat(q)), N * (5 * D + 8))
+    q4 = ops.FloatToFusedNBitRowwiseQuantizedSBHalf(x, 4)
+    rec("FloatToFusedNBitRowwiseQuantizedSBHalf(4) 1Mx128", timeit(lambda: ops.FloatToFusedNBitRowwiseQuantizedSBHalf(x, 4)), N * (4 * D + D // 2 + 4))
+    rec("FusedNBitRowwiseQuantizedSBHalfToFloat(4) 1Mx128", timeit(lambda: ops.FusedNBitRowwiseQuantizedSBHalfToFloat(q4, 4)), N * (4 * D + D // 2 + 4))
+    del x, q, q4
+    B, T = 8192, 512
+    pe = torch.randn(B, T * 128, device=dev).half()
+    perm = torch.randperm(T)
+    off = torch.arange(0, (T + 1) * 128, 128, dtype=torch.int64, device=dev)
+    permd, invd = perm.to(dev), torch.argsort(perm).to(dev)
+    rec("permute_pooled_embs 8192x65536 fp16", timeit(lambda: ops.permute_pooled_embs(pe, off, permd, off, invd)), 2 * pe.numel() * 2)
+    del pe
+    L = torch.randint(0, 64, (1 << 24,), device=dev, dtype=torch.int64)
+    rec("asynchronous_complete_cumsum 16M int64", timeit(lambda: ops.asynchronous_complete_cumsum(L)), 3 * L.numel() * 8)
+    del L
+    T2, B2 = 64, 16384
+    lengths = torch.poisson(torch.full((T2, B2), 32.0, device=dev)).to(torch.int64)
+    tot = int(lengths.sum())
+    vals = torch.arange(tot, device=dev, dtype=torch.int64)
+    p2 = torch.randperm(T2).to(torch.int32).to(dev)
+    rec("permute_2D_sparse_data 64x16384, 33M int64 values", timeit(lambda: ops.permute_2D_sparse_data(p2, lengths, vals, None, tot)),
+        2 * tot * 8 + 2 * lengths.numel() * 8)
+    return res
+
+
 def run_e2e(forward, batches, weighted, steps, index_dtype=None):
     """Same metric through the public call with HOST buffers: every step copies its request (indices, offsets, weights)
     from pinned host memory, runs the step and reads the result back to pinned host memory.  Three streams keep copy-in,
@@ -595,6 +645,26 @@ def run_gpu_arm(args):
         placed_ok = bool(torch.equal(ref, sh[main](b.indices, b.offsets, None)))
         del ref
 
+    input_dist = None
+    if args.input == "feature-major":
+        # every rank starts from the feature-major request of its own B/world samples over ALL tables; the index
+        # all-to-all in front of the lookup turns it into the table-major request of the global batch for its tables
+        from fbgemm_ascend_b200.sharded import FeatureMajorInputDist
+        wl = W.spec("c4", scale_E=args.scale_e, scale_B=args.scale_b, tables=T_glob)
+        wl.B = plan.local_batch
+        fm = W.make_batch(wl, dev, batch_seed=100 + rank, table_ids=list(range(T_glob)))
+        lens_fm = (fm.offsets[1:] - fm.offsets[:-1]).view(T_glob, plan.local_batch)
+        ind = FeatureMajorInputDist(plan, group=dist.group.WORLD if multi else None, device=dev)
+        st = max(3, min(args.steps, 10))
+        for _ in range(2):
+            i_tm, o_tm, _w = ind(lens_fm, fm.indices)
+        ms_dist = allmax(timed(lambda i: ind(lens_fm, fm.indices), st, barrier)) / st
+        ms_both = allmax(timed(lambda i: sh[main](*ind(lens_fm, fm.indices)[:2], None), st, barrier)) / st
+        input_dist = {"ms_per_step": ms_dist, "with_lookup_ms_per_step": ms_both, "rows_per_rank": int(i_tm.numel()),
+                      "what": "permute_2D_sparse_data by owner, lengths + indices all-to-all (one host read of the split sizes), "
+                              "permute_2D_sparse_data to table-major, asynchronous_complete_cumsum"}
+        del fm, lens_fm, i_tm, o_tm
+
     e2e = e2e32 = None
     if not args.no_e2e:
         fwd = lambda i, o, w: sh[main](i, o, w)
@@ -605,6 +675,7 @@ def run_gpu_arm(args):
 
     subs = {}
     cpu = None
+    kernels = None
     if not multi:
         # configuration 4 with int32 indices (the configuration does not fix the index width)
         b32 = [(b.indices.to(torch.int32), b.offsets.to(torch.int32)) for b in batches]
@@ -626,6 +697,11 @@ def run_gpu_arm(args):
                 except Exception as e:
                     subs[sub] = {"error": f"{type(e).__name__}: {e}"[:200]}
                 torch.cuda.empty_cache()
+            try:
+                kernels = second_tier_kernels()
+            except Exception as e:
+                kernels = {"error": f"{type(e).__name__}: {e}"[:200]}
+            torch.cuda.empty_cache()
         if not args.no_cpu:
             try:
                 v, info = cpu_lookup_rate("c4", args.cpu_seconds)
@@ -651,7 +727,7 @@ def run_gpu_arm(args):
                          "peak_kind": peak_kind, "kernel": "tbe_pooled_kernel", "kernel_ms": kern_ms,
                          "algorithmic_bytes_per_launch": acct["algorithmic"], "padded_bytes_per_launch": acct["padded"],
                          "sector_bytes_per_launch": acct["sector"], "frac_of_nominal_8TBs": achieved / 8000.0},
-            "workloads": subs, "cpu_baseline": cpu, "e2e": e2e,
+            "workloads": subs, "kernels": kernels, "input_dist": input_dist, "cpu_baseline": cpu, "e2e": e2e,
             "gpu_launches": args.steps * launches_per_step, "clocks": clocks,
         }
         print(json.dumps(line))
@@ -672,6 +748,9 @@ def main():
     ap.add_argument("--no-subs", action="store_true", help="skip the other configurations (one GPU)")
     ap.add_argument("--exchange", default="both", choices=["both", "direct", "nccl"],
                     help="multi-GPU: peer-store epilogue, NCCL all-to-all + permute kernel, or time both")
+    ap.add_argument("--input", default="table-major", choices=["table-major", "feature-major"],
+                    help="feature-major: also time the index all-to-all that turns every rank's feature-major request into "
+                         "the table-major request the lookup takes")
     ap.add_argument("--scale-e", type=float, default=1.0, help="scale rows per table (small cases for profiling)")
     ap.add_argument("--scale-b", type=float, default=1.0, help="scale the batch size (small cases for profiling)")
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
