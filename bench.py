@@ -100,6 +100,17 @@ class ClockSampler:
         """Marks [t0, t1] as a timed region."""
         self.windows.append((t0, t1))
 
+    def median_mhz(self, t0: float, t1: float):
+        """Median SM clock of the samples taken in [t0, t1] (None without samples)."""
+        v = []
+        for t, l in list(self.lines):
+            if t0 - 0.03 <= t <= t1 + 0.03:
+                try:
+                    v.append(float(l.split(", ")[1]))
+                except Exception:
+                    pass
+        return statistics.median(v) if v else None
+
     def stop(self):
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
@@ -389,8 +400,9 @@ def measure_plain(name, args, sampler, steps, index_dtype=None, scale_e=1.0, sca
         step(i)
     w0 = time.time()
     ms = timed(step, steps) / steps
-    sampler.window(w0, time.time())
     kern = per_launch_ms(step, min(steps, 50))
+    w1 = time.time()
+    sampler.window(w0, w1)
     cold = cold_launch_ms(step)
     acct = [W.algorithmic_bytes(ws, b) for b in batches]
     alg = statistics.mean(a["algorithmic"] for a in acct)
@@ -400,7 +412,7 @@ def measure_plain(name, args, sampler, steps, index_dtype=None, scale_e=1.0, sca
     res = {"ms": kern_ms, "ms_back_to_back": ms, "cold_ms": cold, "rows_per_s": rows / (kern_ms * 1e-3), "rows_per_launch": rows,
            "algorithmic_bytes": alg, "achieved_gbs": alg / (kern_ms * 1e-3) / 1e9, "roofline_frac": alg / (kern_ms * 1e-3) / 1e9 / peak,
            "cold_roofline_frac": alg / (cold * 1e-3) / 1e9 / peak, "table_bytes": W.table_bytes(ws), "launches": steps,
-           "index_dtype": str(ws.index_dtype).split(".")[-1], "build_s": round(build_s, 1), **check}
+           "index_dtype": str(ws.index_dtype).split(".")[-1], "build_s": round(build_s, 1), "sm_mhz": sampler.median_mhz(w0, w1), **check}
     if NCU_DRAM_BYTES_PER_ROW.get(name):
         res["traffic"] = NCU_DRAM_BYTES_PER_ROW[name] * rows
     return res, (tables, batches, ws)
@@ -622,7 +634,9 @@ def run_gpu_arm(args):
         return tables.forward(b.indices, b.offsets, b.weights)
     for i in range(3):
         lookup_only(i)
+    w0 = time.time()
     kern = per_launch_ms(lookup_only, args.steps)
+    kern_mhz = sampler.median_mhz(w0, time.time()) if rank == 0 else None
     kern_ms = allmax(statistics.mean(kern))
     acct = W.algorithmic_bytes(ws, batches[0])
     achieved = acct["algorithmic"] / (kern_ms * 1e-3) / 1e9
@@ -682,10 +696,13 @@ def run_gpu_arm(args):
         f32 = lambda i: sh[main](b32[i % n_batches][0], b32[i % n_batches][1], None)
         for i in range(3):
             f32(i)
+        w0 = time.time()
         k32 = statistics.mean(per_launch_ms(f32, args.steps))
+        w1 = time.time()
+        sampler.window(w0, w1)
         a32 = acct["algorithmic"] - (acct["rows"] + ws.T * ws.B + 1) * 4
         subs["c4_int32"] = {"ms": k32, "rows_per_s": rows_step[0] / (k32 * 1e-3), "algorithmic_bytes": a32,
-                            "roofline_frac": a32 / (k32 * 1e-3) / 1e9 / peak, "e2e": e2e32}
+                            "roofline_frac": a32 / (k32 * 1e-3) / 1e9 / peak, "sm_mhz": sampler.median_mhz(w0, w1), "e2e": e2e32}
         del b32
         if not args.no_subs:
             del sh, tables, batches
@@ -721,7 +738,7 @@ def run_gpu_arm(args):
                         "scale_b": args.scale_b, "build_s": round(build_s, 1), "exchange": main, "index_dtype": "int64"},
             "exchange": results, "exchange_paths_agree": agree, "placement_matches_permute_op": placed_ok,
             "verified": check.get("verified"), "verification": check,
-            "lookup_kernel": {"ms": kern_ms, "cold_ms": cold, "rows_per_s_per_gpu": rows_step[0] / (kern_ms * 1e-3)},
+            "lookup_kernel": {"ms": kern_ms, "cold_ms": cold, "rows_per_s_per_gpu": rows_step[0] / (kern_ms * 1e-3), "sm_mhz": kern_mhz},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "traffic": (NCU_DRAM_BYTES_PER_ROW["c4"] * rows_step[0]) if NCU_DRAM_BYTES_PER_ROW["c4"] else None,
                          "peak_kind": peak_kind, "kernel": "tbe_pooled_kernel", "kernel_ms": kern_ms,

@@ -1092,8 +1092,14 @@ __device__ __noinline__ void pool_run_stream(const LookupParams& p, const TableM
             }
             if (bag_start < lo) write_partial();
             else store_bag(cur, bag_end - bag_start);
+#if defined(TBE_EXP_NOZERO)
+#elif defined(TBE_EXP_MULZERO)
+#pragma unroll
+            for (int s = 0; s < EPL; ++s) acc[s] *= 0.0f;
+#else
 #pragma unroll
             for (int s = 0; s < EPL; ++s) acc[s] = 0.0f;
+#endif
             bias_acc = 0.0f;
             ++cur;
             bag_start = bag_end;
@@ -1115,14 +1121,12 @@ __device__ __noinline__ void pool_run_stream(const LookupParams& p, const TableM
         }
     };
     // Row number narrowed to 32 bits; -1 = nothing to add.  A row outside [-1, 2^31) or past the end of the
-    // table is reported and skipped.
-    const uint64_t avail = static_cast<uint64_t>(m.avail);
+    // table is reported and skipped.  `max_rows` (once per run) folds both limits into one unsigned compare.
+    const uint64_t rows_avail = static_cast<uint64_t>(m.avail) / stride;
+    const uint64_t max_rows = rows_avail < 0x80000000ull ? rows_avail : 0x80000000ull;
     auto narrow = [&](int64_t raw) -> int32_t {
-        if (raw == -1) return -1;
-        const bool bad_range = raw < -1 || raw > 0x7fffffffll;
-        const bool bad_row = !bad_range && static_cast<uint64_t>(raw + 1) * stride > avail;
-        if (bad_range || bad_row) {
-            if (p.error_flag) atomicOr(p.error_flag, bad_range ? 1 : 4);
+        if (static_cast<uint64_t>(raw) >= max_rows) {          // -1 and every other negative number included
+            if (raw != -1 && p.error_flag) atomicOr(p.error_flag, (raw < 0 || raw > 0x7fffffffll) ? 1 : 4);
             return -1;
         }
         return static_cast<int32_t>(raw);
