@@ -139,6 +139,7 @@ __device__ __forceinline__ void cp_async16_ca(uint32_t dst, const void* src, int
 {
     asm volatile("cp.async.ca.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
 }
+#ifdef TBE_L2_HINTS
 // Experiment (TBE_L2_HINTS builds only): the row copies carry an L2 evict-last policy.  Measured on benchmark
 // configurations 2 and 4 (scaled): L2 hit rate, DRAM bytes and kernel time all unchanged (31.8 -> 31.9 % and
 // 45.5 -> 45.5 %; the hottest rows never reach L2, they hit L1, and the rest of the Zipf head stays in L2 anyway),
@@ -153,6 +154,7 @@ __device__ __forceinline__ void cp_async16_ca_hint(uint32_t dst, const void* src
 {
     asm volatile("cp.async.ca.shared.global.L2::cache_hint [%0], [%1], 16, %2, %3;" ::"r"(dst), "l"(src), "r"(bytes), "l"(pol) : "memory");
 }
+#endif
 __device__ __forceinline__ void cp_async8(uint32_t dst, const void* src, int bytes)
 {
     asm volatile("cp.async.ca.shared.global [%0], [%1], 8, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
@@ -781,9 +783,14 @@ __device__ __noinline__ void pool_bag_bytewise(const IdxT* indices, const float*
 __device__ __align__(16) const uint8_t g_zero_row[2048] = {0};
 
 // Read-once streams (indices, per-sample weights): not kept in L1.
-__device__ __forceinline__ int64_t ld_once64(const void* p) { return ld_stream(static_cast<const int64_t*>(p)); }
 __device__ __forceinline__ int32_t ld_once32(const void* p) { return ld_stream(static_cast<const int32_t*>(p)); }
 __device__ __forceinline__ float ld_once_f32(const void* p) { return ld_stream(static_cast<const float*>(p)); }
+__device__ __forceinline__ uint2 ld_once_2x32(const void* p)
+{
+    uint2 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v2.b32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p));
+    return v;
+}
 
 __device__ __forceinline__ void sts16(uint32_t a, float x, float y, float z, float w)
 {
@@ -972,12 +979,13 @@ __device__ __noinline__ void pool_run_stream(const LookupParams& p, const TableM
         const char* op = static_cast<const char*>(p.offsets) + (i0 + lane) * isz;
         off = idx64 ? __ldg(reinterpret_cast<const int64_t*>(op)) : static_cast<int64_t>(__ldg(reinterpret_cast<const int32_t*>(op)));
     }
-    const int64_t R0 = __shfl_sync(kFull, off, 0);
-    const int64_t R1 = __shfl_sync(kFull, off, nb);
+    int64_t R0 = __shfl_sync(kFull, off, 0);
+    int64_t R1 = __shfl_sync(kFull, off, nb);
     if (R0 < 0 || R1 < R0 || R1 > p.num_indices || R1 - R0 > 0x7fffffffll) {
-        // Offsets that do not describe positions of `indices`: nothing is read through them.
+        // Offsets that do not describe positions of `indices`: nothing is read through them; the run's bags are
+        // written as empty ones (zeros), so that the output is defined, and the condition is reported.
         if (p.error_flag && lane == 0) atomicOr(p.error_flag, 8);
-        return;
+        off = R0 = R1 = 0;
     }
     const int n = static_cast<int>(R1 - R0);
     const int rel = static_cast<int>(min(max(off - R0, static_cast<int64_t>(0)), static_cast<int64_t>(n)));
@@ -1111,12 +1119,15 @@ __device__ __noinline__ void pool_run_stream(const LookupParams& p, const TableM
     // Index stream of the group: lane k reads the index (and weight) of row c * LPR + k of the range (chunk c).
     const char* ipb = static_cast<const char*>(p.indices) + (R0 + lo + k) * isz;
     const float* wpb = WEIGHTED ? p.pw + R0 + lo + k : nullptr;
-    auto load_raw = [&](int c, int64_t& raw, float& w) {
-        raw = -1;
+    // The index is kept exactly as loaded (one or two 32-bit words; nothing is computed from it before `narrow` looks
+    // at it two chunks later: even a sign extension right after the load would make the warp wait for the load).
+    auto load_raw = [&](int c, uint2& raw, float& w) {
+        raw = make_uint2(0xffffffffu, 0xffffffffu);
         w = 0.0f;
         if (lo + c * LPR + k < hi) {
             const char* ip = ipb + static_cast<int64_t>(c) * (LPR * isz);
-            raw = idx64 ? ld_once64(ip) : static_cast<int64_t>(ld_once32(ip));
+            if (idx64) raw = ld_once_2x32(ip);
+            else raw.x = static_cast<uint32_t>(ld_once32(ip));
             if constexpr (WEIGHTED) w = ld_once_f32(wpb + c * LPR);
         }
     };
@@ -1124,7 +1135,9 @@ __device__ __noinline__ void pool_run_stream(const LookupParams& p, const TableM
     // table is reported and skipped.  `max_rows` (once per run) folds both limits into one unsigned compare.
     const uint64_t rows_avail = static_cast<uint64_t>(m.avail) / stride;
     const uint64_t max_rows = rows_avail < 0x80000000ull ? rows_avail : 0x80000000ull;
-    auto narrow = [&](int64_t raw) -> int32_t {
+    auto narrow = [&](uint2 words) -> int32_t {
+        const int64_t raw = idx64 ? static_cast<int64_t>((static_cast<uint64_t>(words.y) << 32) | words.x)
+                                  : static_cast<int64_t>(static_cast<int32_t>(words.x));
         if (static_cast<uint64_t>(raw) >= max_rows) {          // -1 and every other negative number included
             if (raw != -1 && p.error_flag) atomicOr(p.error_flag, (raw < 0 || raw > 0x7fffffffll) ? 1 : 4);
             return -1;
@@ -1215,12 +1228,12 @@ __device__ __noinline__ void pool_run_stream(const LookupParams& p, const TableM
     // rolled on purpose: unrolled over the stages (constant stage addresses, one copy of the end-of-bag code per stage)
     // it measured 5-10 % slower, and twice as slow with eight stages -- the loop no longer fits the instruction cache.
     const int total = per + NS;
-    int64_t raw_a, raw_b;                  // the indices of the next chunk and of the one after it, as loaded
+    uint2 raw_a, raw_b;                    // the indices of the next chunk and of the one after it, as loaded
     float w_a = 0.0f, w_b = 0.0f;
     int32_t idx_c;                         // lane k: index of row c * LPR + k of the chunk being requested
     float w_c = 0.0f, w_prev = 0.0f;       // weights of the chunk being requested / of the one before it
     {
-        int64_t raw0;
+        uint2 raw0;
         load_raw(0, raw0, w_c);
         load_raw(1, raw_a, w_a);
         load_raw(2, raw_b, w_b);

@@ -109,7 +109,7 @@ typedef struct {
                                              4  an index at or past the end of its table was met (dev_weights_bytes
                                                 known; the row is skipped like -1 and never read),
                                              8  offsets[T*B] != num_indices, or offsets that point outside
-                                                `indices` (those bags are not read);
+                                                `indices` (such bags are not read and come out as empty ones);
                                            NULL = no reporting (the checks that skip rows are made all the same) */
 } tbe_b200_lookup_args;
 
