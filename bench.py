@@ -35,10 +35,12 @@ if ROOT not in sys.path:
 METRIC = "pooled_lookup_rows_per_s"
 UNIT = "rows/s"
 
-# dram__bytes_read.sum + dram__bytes_write.sum per pooled row of one launch of tbe_pooled_kernel, from single-launch
-# ncu captures of scaled-down cases whose traffic grows with the rows processed (see profiles/); a full launch's
-# traffic is this figure times its rows.  None = not captured for the kernel as it stands.
-NCU_DRAM_BYTES_PER_ROW = {"c2": None, "c3": None, "c4": None, "c5": None}
+# dram__bytes_read.sum + dram__bytes_write.sum of ONE launch of tbe_pooled_kernel at full size, from single-launch ncu
+# captures of the kernel as it stands: configurations 4 and 2 captured at full size (the two counters need
+# one pass), configuration 5 from a capture at 10 % of the rows per table scaled by the rows processed (uniform indices
+# over tables far larger than L2: traffic grows in proportion).  None = not captured.
+NCU_DRAM_BYTES_PER_LAUNCH = {"c2": 168_522_752 + 8_752_384, "c3": None, "c4": 11_639_628_000 + 1_236_728_000,
+                             "c5": int(210.6 * 78_584_431)}
 
 # Benchmark configurations: (tables, rows per table, widths, weight types, batch, bag lengths, index distribution,
 # index type, pooling, output type, weighted, seed) in words, for the `config.workload` label of both arms.
@@ -413,8 +415,8 @@ def measure_plain(name, args, sampler, steps, index_dtype=None, scale_e=1.0, sca
            "algorithmic_bytes": alg, "achieved_gbs": alg / (kern_ms * 1e-3) / 1e9, "roofline_frac": alg / (kern_ms * 1e-3) / 1e9 / peak,
            "cold_roofline_frac": alg / (cold * 1e-3) / 1e9 / peak, "table_bytes": W.table_bytes(ws), "launches": steps,
            "index_dtype": str(ws.index_dtype).split(".")[-1], "build_s": round(build_s, 1), "sm_mhz": sampler.median_mhz(w0, w1), **check}
-    if NCU_DRAM_BYTES_PER_ROW.get(name):
-        res["traffic"] = NCU_DRAM_BYTES_PER_ROW[name] * rows
+    if NCU_DRAM_BYTES_PER_LAUNCH.get(name) and scale_e == 1.0 and scale_b == 1.0:
+        res["traffic"] = NCU_DRAM_BYTES_PER_LAUNCH[name]
     return res, (tables, batches, ws)
 
 
@@ -740,7 +742,8 @@ def run_gpu_arm(args):
             "verified": check.get("verified"), "verification": check,
             "lookup_kernel": {"ms": kern_ms, "cold_ms": cold, "rows_per_s_per_gpu": rows_step[0] / (kern_ms * 1e-3), "sm_mhz": kern_mhz},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "traffic": (NCU_DRAM_BYTES_PER_ROW["c4"] * rows_step[0]) if NCU_DRAM_BYTES_PER_ROW["c4"] else None,
+                         "traffic": NCU_DRAM_BYTES_PER_LAUNCH["c4"] if (args.scale_e == 1.0 and args.scale_b == 1.0) else None,
+                         "traffic_source": "ncu, one launch of this workload at full size (dram__bytes_read.sum + dram__bytes_write.sum)",
                          "peak_kind": peak_kind, "kernel": "tbe_pooled_kernel", "kernel_ms": kern_ms,
                          "algorithmic_bytes_per_launch": acct["algorithmic"], "padded_bytes_per_launch": acct["padded"],
                          "sector_bytes_per_launch": acct["sector"], "frac_of_nominal_8TBs": achieved / 8000.0},

@@ -116,7 +116,10 @@ class TableWiseShardedLookup:
 
     def __init__(self, plan: ShardPlan, tables=None, group=None, exchange: str = "nccl",
                  lookup_fn: Optional[Callable] = None, permute_fn: Optional[Callable] = None,
-                 device: Optional[torch.device] = None, out_dtype: torch.dtype = torch.float16) -> None:
+                 device: Optional[torch.device] = None, out_dtype: torch.dtype = torch.float16,
+                 max_polls: Optional[int] = None) -> None:
+        if max_polls is not None:
+            self.MAX_POLLS = int(max_polls)      # how long a rank waits for its peers' step flags before it reports
         if exchange not in ("nccl", "direct"):
             raise ValueError("exchange must be 'nccl' or 'direct'")
         self.plan = plan
