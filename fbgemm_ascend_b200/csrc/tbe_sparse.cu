@@ -11,6 +11,7 @@
 //
 // Both are streaming integer work bounded by HBM bandwidth.  Both need a little global memory beyond
 // their inputs and outputs (per-tile sums; per-table segment lengths and offsets): the caller passes it.
+#include <cstdlib>
 #include <mutex>
 
 #include "tbe_common.cuh"
@@ -136,6 +137,142 @@ __global__ void __launch_bounds__(kScanThreads) scan_tiles_kernel(const T* __res
     if (blockIdx.x == 0 && threadIdx.x == 0) out[0] = 0;
 #pragma unroll
     for (int j = 0; j < kScanPerThread; ++j)
+        if (first + j * 32 < n) out[first + j * 32 + 1] = static_cast<T>(base + v[j]);
+}
+
+// ---- complete cumsum in one pass: every tile publishes its sum, then looks back over its predecessors ------
+//
+// The three kernels above read the input twice.  Here a tile (4096 elements) reads its part once, publishes the
+// tile's sum ("aggregate", flag 1), collects what lies before it from the descriptors of the tiles in front --
+// stopping at the nearest one that already knows its own prefix ("inclusive", flag 2) -- publishes its inclusive sum
+// and writes its outputs.  Tiles take their number from a ticket counter, so a tile's predecessors are resident or
+// finished when it starts looking: the look-back always makes progress.  Its poll loop is bounded all the same; a
+// tile whose wait runs out adds up the input in front of it by itself (slow, correct), so no error word is needed.
+constexpr int kChainThreads = 256;
+constexpr int kChainPerThread = 16;
+constexpr int kChainTile = kChainThreads * kChainPerThread;
+constexpr int kChainPolls = 1 << 20;      // x >= 32 ns of sleep: tens of milliseconds before a tile gives up
+
+__device__ __forceinline__ int ld_acquire_gpu(const int* p)
+{
+    int v;
+    asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_release_gpu(int* p, int v)
+{
+    asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kChainThreads) chained_scan_kernel(const T* __restrict__ in, int64_t n, T* __restrict__ out,
+                                                                     unsigned* __restrict__ ticket, int* __restrict__ flags,
+                                                                     int64_t* __restrict__ aggregate, int64_t* __restrict__ inclusive,
+                                                                     int max_polls)
+{
+    __shared__ int64_t warp_tot[kChainThreads / 32];
+    __shared__ int64_t red[kChainThreads / 32];
+    __shared__ int64_t s_prefix;
+    __shared__ unsigned s_tile;
+    __shared__ int s_alone;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const bool chained = gridDim.x > 1;
+    if (threadIdx.x == 0) {
+        s_tile = chained ? atomicAdd(ticket, 1u) : 0u;
+        s_alone = 0;
+        s_prefix = 0;
+    }
+    __syncthreads();
+    const int64_t tile = s_tile;
+    const int64_t first = tile * kChainTile + static_cast<int64_t>(warp) * (32 * kChainPerThread) + lane;
+    int64_t v[kChainPerThread];
+#pragma unroll
+    for (int j = 0; j < kChainPerThread; ++j) v[j] = (first + j * 32 < n) ? static_cast<int64_t>(in[first + j * 32]) : 0;
+    int64_t carry = 0;
+#pragma unroll
+    for (int j = 0; j < kChainPerThread; ++j) {
+        int64_t incl = v[j];
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            const int64_t up = __shfl_up_sync(0xffffffffu, incl, d);
+            if (lane >= d) incl += up;
+        }
+        v[j] = carry + incl;
+        carry += __shfl_sync(0xffffffffu, incl, 31);
+    }
+    if (lane == 0) warp_tot[warp] = carry;
+    __syncthreads();
+    int64_t base = 0, total = 0;
+#pragma unroll
+    for (int w = 0; w < kChainThreads / 32; ++w) {
+        const int64_t t = warp_tot[w];
+        if (w < warp) base += t;
+        total += t;
+    }
+    if (chained && warp == 0) {
+        if (tile == 0) {
+            if (lane == 0) {
+                inclusive[0] = total;
+                st_release_gpu(&flags[0], 2);
+            }
+        } else {
+            if (lane == 0) {
+                aggregate[tile] = total;
+                st_release_gpu(&flags[tile], 1);
+            }
+            int64_t acc = 0;
+            int64_t nearest = tile - 1;          // lane 0 looks at this tile, lane l at nearest - l
+            bool gave_up = false;
+            while (true) {
+                const int64_t t = nearest - lane;
+                int f = 2;                         // in front of tile 0: "inclusive sum 0"
+                int polls = 0;
+                while (true) {
+                    f = (t >= 0) ? ld_acquire_gpu(&flags[t]) : 2;
+                    if (__all_sync(0xffffffffu, f != 0)) break;
+                    if (++polls > max_polls) {
+                        gave_up = true;
+                        break;
+                    }
+                    __nanosleep(32);
+                }
+                if (gave_up) break;
+                const int64_t val = (t >= 0) ? (f == 2 ? inclusive[t] : aggregate[t]) : 0;
+                const unsigned known = __ballot_sync(0xffffffffu, f == 2);
+                if (known) {
+                    const int stop = __ffs(known) - 1;          // the nearest tile that knows everything before itself
+                    acc += warp_sum(lane <= stop ? val : 0);
+                    break;
+                }
+                acc += warp_sum(val);
+                nearest -= 32;
+            }
+            if (lane == 0) {
+                if (gave_up) {
+                    s_alone = 1;
+                } else {
+                    s_prefix = acc;
+                    inclusive[tile] = acc + total;
+                    st_release_gpu(&flags[tile], 2);
+                }
+            }
+        }
+    }
+    __syncthreads();
+    int64_t prefix = s_prefix;
+    if (s_alone) {       // block-uniform: the wait ran out, add up everything in front of this tile here
+        int64_t mine = 0;
+        for (int64_t i = threadIdx.x; i < tile * kChainTile; i += kChainThreads) mine += static_cast<int64_t>(in[i]);
+        prefix = block_sum(mine, red);
+        if (threadIdx.x == 0) {
+            inclusive[tile] = prefix + total;
+            st_release_gpu(&flags[tile], 2);
+        }
+    }
+    base += prefix;
+    if (tile == 0 && threadIdx.x == 0) out[0] = 0;
+#pragma unroll
+    for (int j = 0; j < kChainPerThread; ++j)
         if (first + j * 32 < n) out[first + j * 32 + 1] = static_cast<T>(base + v[j]);
 }
 
@@ -311,12 +448,51 @@ int complete_cumsum_launch(const void* in, int64_t n, int index_bits, void* out,
 
 int64_t complete_cumsum_tiles(int64_t n) { return (n + kScanTile - 1) / kScanTile; }
 
+// One-pass form.  Scratch: [ticket, 16 bytes][flags, 4 bytes per tile, padded to 16][aggregate, 8 per tile][inclusive, 8 per tile];
+// the ticket and the flags are cleared on the stream in front of the kernel.
+int64_t chained_tiles(int64_t n) { return (n + kChainTile - 1) / kChainTile; }
+int64_t chained_flag_bytes(int64_t tiles) { return 16 + ((tiles * 4 + 15) / 16) * 16; }
+int64_t chained_scratch_bytes(int64_t n)
+{
+    const int64_t tiles = chained_tiles(n);
+    return tiles > 1 ? chained_flag_bytes(tiles) + tiles * 16 : 0;
+}
+int chained_polls()
+{
+    const char* v = getenv("TBE_B200_SCAN_POLLS");     // 0 makes every tile add up its own prefix (tests)
+    static const int polls = (v && *v) ? atoi(v) : kChainPolls;
+    return polls;
+}
+int complete_cumsum_chained_launch(const void* in, int64_t n, int index_bits, void* out, void* scratch, cudaStream_t s)
+{
+    const int64_t tiles = chained_tiles(n);
+    unsigned char* base = static_cast<unsigned char*>(scratch);
+    unsigned* ticket = nullptr;
+    int* flags = nullptr;
+    int64_t *aggregate = nullptr, *inclusive = nullptr;
+    if (tiles > 1) {
+        const int64_t fb = chained_flag_bytes(tiles);
+        if (cudaMemsetAsync(base, 0, static_cast<size_t>(fb), s) != cudaSuccess) return fail(TBE_B200_ERR_CUDA, "complete_cumsum: memset failed");
+        ticket = reinterpret_cast<unsigned*>(base);
+        flags = reinterpret_cast<int*>(base + 16);
+        aggregate = reinterpret_cast<int64_t*>(base + fb);
+        inclusive = aggregate + tiles;
+    }
+    const int polls = chained_polls();
+    if (index_bits == 32)
+        chained_scan_kernel<int32_t><<<static_cast<unsigned>(tiles), kChainThreads, 0, s>>>(static_cast<const int32_t*>(in), n, static_cast<int32_t*>(out),
+                                                                                           ticket, flags, aggregate, inclusive, polls);
+    else
+        chained_scan_kernel<int64_t><<<static_cast<unsigned>(tiles), kChainThreads, 0, s>>>(static_cast<const int64_t*>(in), n, static_cast<int64_t*>(out),
+                                                                                           ticket, flags, aggregate, inclusive, polls);
+    return check_launch("complete_cumsum");
+}
+
 }  // namespace tbe
 
 extern "C" int64_t tbe_b200_complete_cumsum_scratch_bytes(int64_t n)
 {
-    const int64_t tiles = tbe::complete_cumsum_tiles(n < 0 ? 0 : n);
-    return tiles > 1 ? tiles * 8 : 0;
+    return tbe::chained_scratch_bytes(n < 0 ? 0 : n);
 }
 
 extern "C" int tbe_b200_complete_cumsum(const void* in, int64_t n, int index_bits, void* out, void* scratch, int64_t scratch_bytes,
@@ -336,8 +512,8 @@ extern "C" int tbe_b200_complete_cumsum(const void* in, int64_t n, int index_bit
     if (need > 0 && (!scratch || scratch_bytes < need))
         return fail(TBE_B200_ERR_INVALID_ARGUMENT, "complete_cumsum: %lld bytes of scratch are needed, got %lld", static_cast<long long>(need),
                     static_cast<long long>(scratch ? scratch_bytes : 0));
-    if (complete_cumsum_tiles(n) > 0x7fffffffll) return fail(TBE_B200_ERR_UNSUPPORTED, "complete_cumsum: too many elements for one launch");
-    return complete_cumsum_launch(in, n, index_bits, out, static_cast<int64_t*>(scratch), s);
+    if (chained_tiles(n) > 0x7fffffffll) return fail(TBE_B200_ERR_UNSUPPORTED, "complete_cumsum: too many elements for one launch");
+    return complete_cumsum_chained_launch(in, n, index_bits, out, scratch, s);
 }
 
 extern "C" int64_t tbe_b200_permute_2d_sparse_scratch_bytes(int64_t T_in, int64_t T_out)
