@@ -458,7 +458,7 @@ def second_tier_kernels() -> dict:
     rec("permute_pooled_embs 8192x65536 fp16", timeit(lambda: ops.permute_pooled_embs(pe, off, permd, off, invd)), 2 * pe.numel() * 2)
     del pe
     L = torch.randint(0, 64, (1 << 24,), device=dev, dtype=torch.int64)
-    rec("asynchronous_complete_cumsum 16M int64", timeit(lambda: ops.asynchronous_complete_cumsum(L)), 3 * L.numel() * 8)
+    rec("asynchronous_complete_cumsum 16M int64", timeit(lambda: ops.asynchronous_complete_cumsum(L)), 2 * L.numel() * 8)
     del L
     T2, B2 = 64, 16384
     lengths = torch.poisson(torch.full((T2, B2), 32.0, device=dev)).to(torch.int64)

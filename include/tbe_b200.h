@@ -187,9 +187,11 @@ int tbe_b200_permute_pooled_embs_blocked(const void* pooled_embs, int64_t B, int
  * index_bits (32 or 64) bits, `out` n + 1 of the same type (sums wrap like the integer type does).
  * Replaces aclnnAsynchronousCompleteCumsum, reached from asynchronous_complete_cumsum_npu
  * (src/sparse_ops/asynchronous_complete_cumsum/asynchronous_complete_cumsum.cpp:14-37); the inclusive and
- * exclusive forms (:39-57) are views of this result.  Inputs longer than one tile need scratch:
+ * exclusive forms (:39-57) are views of this result.  Inputs longer than 8192 elements need scratch:
  * tbe_b200_complete_cumsum_scratch_bytes(n) bytes of device memory (0 for short inputs, then scratch may be
- * NULL), 8-byte aligned, overwritten by the call. */
+ * NULL; 16 bytes per 8192 elements otherwise), 8-byte aligned, overwritten by the call.  The call puts one small
+ * memset of the scratch and one kernel on the stream; the input is read once.  Two calls that may overlap need
+ * separate scratch. */
 int64_t tbe_b200_complete_cumsum_scratch_bytes(int64_t n);
 int tbe_b200_complete_cumsum(const void* in, int64_t n, int index_bits, void* out, void* scratch, int64_t scratch_bytes,
                              tbe_b200_stream_t stream);

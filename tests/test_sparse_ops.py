@@ -47,7 +47,7 @@ def _rng(*key):
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("dtype", [np.int32, np.int64])
-@pytest.mark.parametrize("length", [0, 1, 10, 100, 1000, 1024, 2048, 2049, 10000, 20000, 1 << 20, (1 << 22) + 77])
+@pytest.mark.parametrize("length", [0, 1, 10, 100, 1000, 1024, 2048, 2049, 8192, 8193, 16384, 16385, 20000, 1 << 20, (1 << 22) + 77])
 @pytest.mark.parametrize("ns", ["fbgemm", "mxrec"])
 def test_cumsum_ops(dtype, length, ns):
     import torch
@@ -78,6 +78,53 @@ def test_cumsum_wraps_and_rejects():
     out = torch.empty(10001, dtype=torch.int64, device="cuda")
     rc = cabi.lib().tbe_b200_complete_cumsum(t.data_ptr(), 10000, 64, out.data_ptr(), None, 0, None)
     assert rc != 0 and "scratch" in cabi.last_error()
+
+
+@pytest.mark.gpu
+def test_cumsum_large_and_signed():
+    """16.8 M elements (2048 tiles looking back over one another) with negative entries, and int64 sums that wrap."""
+    import torch
+    import fbgemm_ascend_b200  # noqa: F401
+
+    x = _rng("cumsum-large").integers(-50, 100, (1 << 24) + 5).astype(np.int64)
+    got = torch.ops.fbgemm.asynchronous_complete_cumsum(torch.from_numpy(x).cuda()).cpu().numpy()
+    assert np.array_equal(got, O.complete_cumsum(x))
+    # a view that starts one element into its storage: not 16-byte aligned, staged element by element
+    for dt in (np.int32, np.int64):
+        z = _rng("cumsum-unaligned", dt.__name__).integers(0, 1000, 70_001).astype(dt)
+        view = torch.from_numpy(z).cuda()[1:]
+        assert view.data_ptr() % 16 != 0
+        assert np.array_equal(torch.ops.fbgemm.asynchronous_complete_cumsum(view).cpu().numpy(), O.complete_cumsum(z[1:]))
+    y = _rng("cumsum-wrap").integers(-2**62, 2**62, 100_000).astype(np.int64)
+    got = torch.ops.fbgemm.asynchronous_complete_cumsum(torch.from_numpy(y).cuda()).cpu().numpy()
+    with np.errstate(over="ignore"):
+        assert np.array_equal(got, O.complete_cumsum(y))
+
+
+_ALONE = """
+import sys, numpy as np, torch
+sys.path.insert(0, {root!r})
+import fbgemm_ascend_b200, oracle as O
+for dt in (np.int32, np.int64):
+    for n in (8193, 50_000, 300_001):
+        x = np.random.default_rng(n).integers(0, 100, n).astype(dt)
+        got = torch.ops.fbgemm.asynchronous_complete_cumsum(torch.from_numpy(x).cuda()).cpu().numpy()
+        assert np.array_equal(got, O.complete_cumsum(x)), (dt, n)
+print("alone-ok")
+"""
+
+
+@pytest.mark.gpu
+def test_cumsum_tile_whose_wait_runs_out_adds_up_its_prefix_itself():
+    """With a poll limit of 0 no tile ever waits for the tiles in front of it: each one falls back to summing the
+    input before it, and the result is the same."""
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, TBE_B200_SCAN_POLLS="0")
+    r = subprocess.run([sys.executable, "-c", _ALONE.format(root=root)], env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0 and "alone-ok" in r.stdout, r.stdout[-500:] + r.stderr[-1500:]
 
 
 VTYPES = ["int64", "int32", "float32", "float16", "bfloat16"]
