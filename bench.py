@@ -449,7 +449,19 @@ def second_tier_kernels() -> dict:
     q4 = ops.FloatToFusedNBitRowwiseQuantizedSBHalf(x, 4)
     rec("FloatToFusedNBitRowwiseQuantizedSBHalf(4) 1Mx128", timeit(lambda: ops.FloatToFusedNBitRowwiseQuantizedSBHalf(x, 4)), N * (4 * D + D // 2 + 4))
     rec("FusedNBitRowwiseQuantizedSBHalfToFloat(4) 1Mx128", timeit(lambda: ops.FusedNBitRowwiseQuantizedSBHalfToFloat(q4, 4)), N * (4 * D + D // 2 + 4))
-    del x, q, q4
+    from fbgemm_ascend_b200 import cabi, workloads as W
+    from fbgemm_ascend_b200.types import PoolingMode, SparseType
+    rows = torch.empty(N * 144, dtype=torch.uint8, device=dev)
+    rec("quantize_to_table_rows INT8 1Mx128", timeit(lambda: cabi.quantize_to_table_rows(x, int(SparseType.INT8), 144, rows)), N * (4 * D + 144))
+    del x, q, q4, rows
+    # sequence lookup (no pooling): every looked-up row is dequantised and written out, fp16
+    ws = W.spec("c2")
+    ws.pooling, ws.output_dtype = PoolingMode.NONE, SparseType.FP16
+    seq = W.build_tables(ws, dev)
+    sb = [W.make_batch(ws, dev, batch_seed=i) for i in range(2)]
+    rec("sequence lookup (pooling NONE) 26 x 1M x 128 INT8 -> fp16, 1.6M rows",
+        timeit(lambda: seq.forward(sb[0].indices, sb[0].offsets, None)), sb[0].num_rows * (144 + 8 + 2 * D))
+    del seq, sb
     B, T = 8192, 512
     pe = torch.randn(B, T * 128, device=dev).half()
     perm = torch.randperm(T)

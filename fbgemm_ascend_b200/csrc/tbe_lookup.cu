@@ -1543,10 +1543,29 @@ __device__ __noinline__ void nobag_position_bytewise(const LookupParams& p, cons
     for (int e = m.D + lane; e < max_D; e += kWarp) store_scalar(seg, e, 0.0f, p.out_ty);
 }
 
+// Four consecutive output elements of a row image in shared memory (e0 a multiple of 4).
+__device__ __forceinline__ void stage_out4(uint8_t* row_image, int e0, const float* v, int out_ty)
+{
+    if (out_ty == TBE_B200_FP32) {
+        *reinterpret_cast<float4*>(row_image + e0 * 4) = make_float4(v[0], v[1], v[2], v[3]);
+    } else {
+        uint32_t h[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) h[j] = (out_ty == TBE_B200_FP16) ? f32_to_f16_bits(v[j]) : f32_to_bf16_bits(v[j]);
+        *reinterpret_cast<uint2*>(row_image + e0 * 2) = make_uint2(h[0] | (h[1] << 16), h[2] | (h[3] << 16));
+    }
+}
+
+constexpr int kNobagStageBytes = 2048;   // the G rows of one step: at most 512 elements of 4 bytes
+
 // `cnt` consecutive positions [n, n + cnt) of one table with aligned rows of D = 16 * units <= 512 elements.
+// A lane's 16 decoded elements start 4 (INT8) or 8 (INT4) elements before a 16-element boundary, so stored from
+// registers they are 8-byte pieces 32 bytes apart: every 32-byte sector of the output -- which is larger than the
+// input here -- is written in part by several instructions.  With a 16-byte aligned output the G rows of a step are
+// put together in the warp's `stage` area and leave as whole 16-byte pieces, consecutive from lane to lane.
 template <int TY, int LPR, typename IdxT>
 __device__ __forceinline__ void nobag_rows(const LookupParams& p, const TableMeta& m, const IdxT* indices, int64_t n, int cnt, int max_D,
-                                           int lane)
+                                           int lane, uint8_t* stage)
 {
     constexpr bool kHdr = (TY == TBE_B200_INT8 || TY == TBE_B200_INT4);
     constexpr bool k8 = (TY == TBE_B200_INT8);
@@ -1560,37 +1579,57 @@ __device__ __forceinline__ void nobag_rows(const LookupParams& p, const TableMet
     const bool head_lane = kHdr && k == 0;
     const bool active = k < nunits;
     const int esz = (p.out_ty == TBE_B200_FP32) ? 4 : 2;
-    for (int r0 = 0; r0 < cnt; r0 += G) {
-        const bool mine = r0 + g < cnt;
-        int64_t idx = -1;
-        if (mine) {
-            idx = static_cast<int64_t>(__ldg(indices + n + r0 + g));
-            if ((idx < -1 || idx > 0x7fffffffll) && k == 0 && p.error_flag) atomicOr(p.error_flag, 1);
-            if (idx > 0x7fffffffll) idx = -1;
-            if (idx >= 0 && static_cast<uint64_t>(idx + 1) * static_cast<uint64_t>(m.stride) > static_cast<uint64_t>(m.avail)) {
-                if (k == 0 && p.error_flag) atomicOr(p.error_flag, 4);
-                idx = -1;
-            }
+    const int row_out_bytes = D * esz, pieces_per_row = row_out_bytes / 16;
+    const bool staged = (reinterpret_cast<uintptr_t>(p.output) & 15) == 0 && (p.out_stride * esz) % 16 == 0;   // warp-uniform
+    // The warp's positions are narrowed and checked once (lane l holds positions l and l + 32), then taken U steps of
+    // G rows at a time: the row loads of all U steps are issued before the first row is decoded, so U * G rows per warp
+    // are in flight instead of G.
+    constexpr int U = (NCH == 1) ? 4 : (NCH == 2 ? 2 : 1);
+    auto checked = [&](int pos) -> int32_t {
+        if (pos >= cnt) return -1;
+        int64_t idx = static_cast<int64_t>(__ldg(indices + n + pos));
+        if ((idx < -1 || idx > 0x7fffffffll) && p.error_flag) atomicOr(p.error_flag, 1);
+        if (idx > 0x7fffffffll || idx < 0) return -1;
+        if (static_cast<uint64_t>(idx + 1) * static_cast<uint64_t>(m.stride) > static_cast<uint64_t>(m.avail)) {
+            if (p.error_flag) atomicOr(p.error_flag, 4);
+            return -1;
         }
-        const bool ok = idx >= 0;
-        const uint8_t* row = m.table + (ok ? idx : 0) * m.stride;
-        uint32_t words[4 * NCH];
+        return static_cast<int32_t>(idx);
+    };
+    const int32_t idx_lo = checked(lane), idx_hi = checked(lane + 32);
+    for (int r0 = 0; r0 < cnt; r0 += G * U) {
+        uint32_t words_u[U][4 * NCH];
+        uint32_t tail_u[U];
 #pragma unroll
-        for (int c = 0; c < 4 * NCH; ++c) words[c] = 0u;
-        uint32_t tail = 0u;
-        if (ok && active) {
-            if constexpr (TY == TBE_B200_INT4) {
-                const uint2 v = ldg8(row + k * 8);
-                words[0] = v.x; words[1] = v.y;
-            } else {
+        for (int u = 0; u < U; ++u) {
+            const int pos = r0 + u * G + g;
+            const int32_t a = __shfl_sync(kFull, idx_lo, pos & 31), b = __shfl_sync(kFull, idx_hi, pos & 31);
+            const int32_t idx = pos < 32 ? a : (pos < 64 ? b : -1);
+            const bool ok = idx >= 0;
+            const uint8_t* row = m.table + static_cast<int64_t>(ok ? idx : 0) * m.stride;
 #pragma unroll
-                for (int c = 0; c < NCH; ++c) {
-                    const uint4 v = ldg16(row + 16 * (k + c * nunits));
-                    words[4 * c + 0] = v.x; words[4 * c + 1] = v.y; words[4 * c + 2] = v.z; words[4 * c + 3] = v.w;
+            for (int c = 0; c < 4 * NCH; ++c) words_u[u][c] = 0u;
+            tail_u[u] = 0u;
+            if (ok && active) {
+                if constexpr (TY == TBE_B200_INT4) {
+                    const uint2 v = ldg8(row + k * 8);
+                    words_u[u][0] = v.x; words_u[u][1] = v.y;
+                } else {
+#pragma unroll
+                    for (int c = 0; c < NCH; ++c) {
+                        const uint4 v = ldg16(row + 16 * (k + c * nunits));
+                        words_u[u][4 * c + 0] = v.x; words_u[u][4 * c + 1] = v.y; words_u[u][4 * c + 2] = v.z; words_u[u][4 * c + 3] = v.w;
+                    }
                 }
+                if (head_lane) tail_u[u] = ldg4(row + (k8 ? D : D / 2));
             }
-            if (head_lane) tail = ldg4(row + (k8 ? D : D / 2));
         }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+        const uint32_t* words = words_u[u];
+        const uint32_t tail = tail_u[u];
+        const int pos = r0 + u * G + g;
+        const bool mine = pos < cnt;
         float v[16];
         if constexpr (kHdr) {
             const uint32_t hdr = __shfl_sync(kFull, words[0], 0, LPR);   // zero for a row that is not read
@@ -1637,8 +1676,32 @@ __device__ __forceinline__ void nobag_rows(const LookupParams& p, const TableMet
 #pragma unroll
             for (int s = 0; s < 16; ++s) v[s] = __uint_as_float(words[s]);
         }
-        if (mine) {
-            char* seg = static_cast<char*>(p.output) + (n + r0 + g) * p.out_stride * esz;
+        if (staged) {
+            if (active) {
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const int slot = 4 * q;
+                    int e0;
+                    if constexpr (kHdr) e0 = (head_lane && slot < HS) ? (D - HS + slot) : (16 * k - HS + slot);
+                    else e0 = EPC * (k + (slot / EPC) * nunits) + (slot % EPC);
+                    stage_out4(stage + g * row_out_bytes, e0, &v[slot], p.out_ty);
+                }
+            }
+            __syncwarp();
+            for (int c = lane; c < G * pieces_per_row; c += kWarp) {
+                const int row = c / pieces_per_row, piece = c - row * pieces_per_row;
+                const int rpos = r0 + u * G + row;
+                if (rpos < cnt)
+                    st_stream16(static_cast<char*>(p.output) + (n + rpos) * p.out_stride * esz + 16 * piece,
+                                *reinterpret_cast<const uint4*>(stage + row * row_out_bytes + 16 * piece));
+            }
+            __syncwarp();
+            if (mine) {
+                char* seg = static_cast<char*>(p.output) + (n + pos) * p.out_stride * esz;
+                for (int e = D + k; e < max_D; e += LPR) store_scalar(seg, e, 0.0f, p.out_ty);
+            }
+        } else if (mine) {
+            char* seg = static_cast<char*>(p.output) + (n + pos) * p.out_stride * esz;
             const bool vec = ((reinterpret_cast<uintptr_t>(seg)) & 15) == 0;
             if (active) {
 #pragma unroll
@@ -1652,24 +1715,27 @@ __device__ __forceinline__ void nobag_rows(const LookupParams& p, const TableMet
             }
             for (int e = D + k; e < max_D; e += LPR) store_scalar(seg, e, 0.0f, p.out_ty);
         }
+        }
     }
 }
 
 template <int TY, typename IdxT>
 __device__ __forceinline__ void nobag_rows_by_width(const LookupParams& p, const TableMeta& m, const IdxT* indices, int64_t n, int cnt,
-                                                    int max_D, int lane)
+                                                    int max_D, int lane, uint8_t* stage)
 {
     const int nunits = m.D / 16;
-    if (nunits <= 4) nobag_rows<TY, 4, IdxT>(p, m, indices, n, cnt, max_D, lane);
-    else if (nunits <= 8) nobag_rows<TY, 8, IdxT>(p, m, indices, n, cnt, max_D, lane);
-    else if (nunits <= 16) nobag_rows<TY, 16, IdxT>(p, m, indices, n, cnt, max_D, lane);
-    else nobag_rows<TY, 32, IdxT>(p, m, indices, n, cnt, max_D, lane);
+    if (nunits <= 4) nobag_rows<TY, 4, IdxT>(p, m, indices, n, cnt, max_D, lane, stage);
+    else if (nunits <= 8) nobag_rows<TY, 8, IdxT>(p, m, indices, n, cnt, max_D, lane, stage);
+    else if (nunits <= 16) nobag_rows<TY, 16, IdxT>(p, m, indices, n, cnt, max_D, lane, stage);
+    else nobag_rows<TY, 32, IdxT>(p, m, indices, n, cnt, max_D, lane, stage);
 }
 
 template <typename IdxT>
 __global__ void __launch_bounds__(kWarpsPerBlock* kWarp)
 tbe_nobag_kernel(const __grid_constant__ LookupParams p, int64_t num_indices, int max_D)
 {
+    __shared__ __align__(16) uint8_t stage_all[kWarpsPerBlock][kNobagStageBytes];
+    uint8_t* stage = stage_all[threadIdx.x >> 5];
     const int lane = threadIdx.x & 31;
     const int64_t gw = static_cast<int64_t>(blockIdx.x) * kWarpsPerBlock + (threadIdx.x >> 5);
     int64_t n = gw * kNobagChunk;
@@ -1700,11 +1766,11 @@ tbe_nobag_kernel(const __grid_constant__ LookupParams p, int64_t num_indices, in
         bool done = fast;
         if (fast) {
             switch (m.ty) {
-                case TBE_B200_INT8: nobag_rows_by_width<TBE_B200_INT8, IdxT>(p, m, indices, n, cnt, max_D, lane); break;
-                case TBE_B200_INT4: nobag_rows_by_width<TBE_B200_INT4, IdxT>(p, m, indices, n, cnt, max_D, lane); break;
-                case TBE_B200_FP8: nobag_rows_by_width<TBE_B200_FP8, IdxT>(p, m, indices, n, cnt, max_D, lane); break;
-                case TBE_B200_FP16: nobag_rows_by_width<TBE_B200_FP16, IdxT>(p, m, indices, n, cnt, max_D, lane); break;
-                case TBE_B200_FP32: nobag_rows_by_width<TBE_B200_FP32, IdxT>(p, m, indices, n, cnt, max_D, lane); break;
+                case TBE_B200_INT8: nobag_rows_by_width<TBE_B200_INT8, IdxT>(p, m, indices, n, cnt, max_D, lane, stage); break;
+                case TBE_B200_INT4: nobag_rows_by_width<TBE_B200_INT4, IdxT>(p, m, indices, n, cnt, max_D, lane, stage); break;
+                case TBE_B200_FP8: nobag_rows_by_width<TBE_B200_FP8, IdxT>(p, m, indices, n, cnt, max_D, lane, stage); break;
+                case TBE_B200_FP16: nobag_rows_by_width<TBE_B200_FP16, IdxT>(p, m, indices, n, cnt, max_D, lane, stage); break;
+                case TBE_B200_FP32: nobag_rows_by_width<TBE_B200_FP32, IdxT>(p, m, indices, n, cnt, max_D, lane, stage); break;
                 default: done = false; break;
             }
         }
