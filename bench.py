@@ -688,10 +688,48 @@ def run_gpu_arm(args):
             i_tm, o_tm, _w = ind(lens_fm, fm.indices)
         ms_dist = allmax(timed(lambda i: ind(lens_fm, fm.indices), st, barrier)) / st
         ms_both = allmax(timed(lambda i: sh[main](*ind(lens_fm, fm.indices)[:2], None), st, barrier)) / st
+        ind.stages = []
+        ind(lens_fm, fm.indices)
+        stages = ind.stage_ms()
+        ind.stages = None
+        # the same with the indices narrowed to int32 first (row numbers fit 31 bits): half the bytes permuted and
+        # exchanged, and the lookup takes int32 indices and offsets
+        ind32 = FeatureMajorInputDist(plan, group=dist.group.WORLD if multi else None, device=dev, index_dtype=torch.int32,
+                                      wire_dtype=torch.int32)
+        for _ in range(2):
+            i32, o32, _w = ind32(lens_fm, fm.indices)
+        same32 = bool(allsum(0.0 if (torch.equal(i32, i_tm.to(torch.int32)) and torch.equal(o32, o_tm.to(torch.int32))) else 1.0) == 0.0)
+        ms_dist32 = allmax(timed(lambda i: ind32(lens_fm, fm.indices), st, barrier)) / st
+        ms_both32 = allmax(timed(lambda i: sh[main](*ind32(lens_fm, fm.indices)[:2], None), st, barrier)) / st
+        ind32.stages = []
+        ind32(lens_fm, fm.indices)
+        stages32 = ind32.stage_ms()
+        direct = None
+        if multi:
+            # the exchange folded into the first permute: every owner's indices are stored straight into a slot of that
+            # owner's receive buffer (peer memory), step flags instead of the index all-to-all
+            cap = int(fm.indices.numel() / world * 1.05) + 1024
+            res_d = {}
+            for name, kw in (("int64", {}), ("int32_wire", dict(wire_dtype=torch.int32, index_dtype=torch.int32))):
+                ind_d = FeatureMajorInputDist(plan, group=dist.group.WORLD, device=dev, exchange="direct", slot_capacity=cap, **kw)
+                for _ in range(2):
+                    i_d, o_d, _w = ind_d(lens_fm, fm.indices)
+                same = bool(allsum(0.0 if (torch.equal(i_d, i_tm.to(i_d.dtype)) and torch.equal(o_d, o_tm.to(o_d.dtype))) else 1.0) == 0.0)
+                ms_d = allmax(timed(lambda i: ind_d(lens_fm, fm.indices), st, barrier)) / st
+                ms_db = allmax(timed(lambda i: sh[main](*ind_d(lens_fm, fm.indices)[:2], None), st, barrier)) / st
+                ind_d.stages = []
+                ind_d(lens_fm, fm.indices)
+                res_d[name] = {"ms_per_step": ms_d, "with_lookup_ms_per_step": ms_db, "same_request": same,
+                               "status": int(allsum(float(ind_d.check_status()))), "stages_ms_rank0": ind_d.stage_ms()}
+                del ind_d, i_d, o_d
+            direct = res_d
         input_dist = {"ms_per_step": ms_dist, "with_lookup_ms_per_step": ms_both, "rows_per_rank": int(i_tm.numel()),
+                      "stages_ms_rank0": stages, "peer_store_exchange": direct,
+                      "int32_wire": {"ms_per_step": ms_dist32, "with_lookup_ms_per_step": ms_both32, "same_request": same32,
+                                     "stages_ms_rank0": stages32},
                       "what": "permute_2D_sparse_data by owner, lengths + indices all-to-all (one host read of the split sizes), "
                               "permute_2D_sparse_data to table-major, asynchronous_complete_cumsum"}
-        del fm, lens_fm, i_tm, o_tm
+        del fm, lens_fm, i_tm, o_tm, i32, o32
 
     e2e = e2e32 = None
     if not args.no_e2e:

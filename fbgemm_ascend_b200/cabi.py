@@ -46,6 +46,7 @@ EXPORTS = {
     "tbe_b200_permute_2d_sparse_scratch_bytes": (_i64, [_i64, _i64]),
     "tbe_b200_permute_2d_sparse_offsets": (_i32, [_vp, _i64, _vp, _i32, _i64, _i64, _vp, _vp, _i64, _vp, _vp]),
     "tbe_b200_permute_2d_sparse_copy": (_i32, [_vp, _i64, _i64, _vp, _i64, _vp, _i64, _vp, _vp, _i64, _vp, _vp]),
+    "tbe_b200_permute_2d_sparse_copy_to_dests": (_i32, [_vp, _i64, _i64, _vp, _i64, _vp, _i64, _i64, _i64, _vp, _vp, _vp]),
     "tbe_b200_signal_peers": (_i32, [_vp, _i32, _i32, _i64, _vp]),
     "tbe_b200_wait_flags": (_i32, [_vp, _i32, _i64, _i64, _vp, _vp]),
     "tbe_b200_last_error": (C.c_char_p, []),
@@ -168,6 +169,36 @@ def permute_pooled_embs_blocked(blocks: torch.Tensor, offset_dim_list: torch.Ten
                                                      _ptr(inv_offset_dim_list), permute_list.numel(), _ptr(output),
                                                      _ptr(error_flag), _stream()), "tbe_b200_permute_pooled_embs_blocked")
     return output
+
+
+def permute_2d_sparse_offsets(permute: torch.Tensor, lengths: torch.Tensor, scratch: torch.Tensor,
+                              error_flag: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``tbe_b200_permute_2d_sparse_offsets`` on the current stream: returns ``lengths[permute]`` ([T_out, B]) and leaves
+    the segment offsets in ``scratch`` (int64, at least ``permute_2d_sparse_scratch_elems(T_in, T_out)`` entries)."""
+    assert permute.dtype == torch.int32 and lengths.dim() == 2 and lengths.is_contiguous() and scratch.dtype == torch.int64
+    T_in, B = lengths.shape
+    T_out = permute.numel()
+    out = torch.empty((T_out, B), dtype=lengths.dtype, device=lengths.device)
+    check(lib().tbe_b200_permute_2d_sparse_offsets(_ptr(permute), T_out, _ptr(lengths), 32 if lengths.dtype == torch.int32 else 64,
+                                                   T_in, B, _ptr(out), _ptr(scratch), scratch.numel() * 8, _ptr(error_flag), _stream()),
+          "tbe_b200_permute_2d_sparse_offsets")
+    return out
+
+
+def permute_2d_sparse_scratch_elems(T_in: int, T_out: int) -> int:
+    return (lib().tbe_b200_permute_2d_sparse_scratch_bytes(T_in, T_out) + 7) // 8
+
+
+def permute_2d_sparse_copy_to_dests(permute: torch.Tensor, T_in: int, values: torch.Tensor, dest_bases: torch.Tensor,
+                                    tables_per_dest: int, dest_capacity: int, scratch: torch.Tensor,
+                                    error_flag: Optional[torch.Tensor] = None) -> None:
+    """``tbe_b200_permute_2d_sparse_copy_to_dests`` on the current stream; ``dest_bases`` is an int64 CUDA tensor of
+    addresses (local or peer memory), ``scratch`` what :func:`permute_2d_sparse_offsets` left."""
+    assert values.is_contiguous() and dest_bases.dtype == torch.int64
+    vb = values.element_size() * (values.numel() // max(values.shape[0], 1) if values.dim() > 1 else 1)
+    check(lib().tbe_b200_permute_2d_sparse_copy_to_dests(_ptr(permute), permute.numel(), T_in, _ptr(values), vb, _ptr(dest_bases),
+                                                         tables_per_dest, dest_capacity, values.shape[0], _ptr(scratch), _ptr(error_flag),
+                                                         _stream()), "tbe_b200_permute_2d_sparse_copy_to_dests")
 
 
 def signal_peers(peer_flag_ptrs: torch.Tensor, world: int, rank: int, value: int) -> None:

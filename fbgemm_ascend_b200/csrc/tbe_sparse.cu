@@ -518,6 +518,50 @@ __global__ void __launch_bounds__(256) permute_segments_kernel(const VT* __restr
     }
 }
 
+// The same walk, but the output tables go to several buffers: output table i belongs to destination i / tables_per_dest
+// and lands at (its position within that destination's group of tables) in dest_bases[destination] -- which may be a
+// peer GPU's memory: plain stores over NVLink, the exchange of an all-to-all folded into the permute.  A destination
+// takes at most dest_capacity positions; what does not fit is dropped and reported.
+template <typename VT>
+__global__ void __launch_bounds__(256) permute_segments_to_dests_kernel(const VT* __restrict__ src, const int64_t* __restrict__ dest_bases,
+                                                                        int64_t tables_per_dest, int64_t dest_capacity, int64_t units_per_pos,
+                                                                        const int32_t* __restrict__ permute, int64_t T_in, int64_t T_out,
+                                                                        const int64_t* __restrict__ in_off, const int64_t* __restrict__ out_off,
+                                                                        int32_t* __restrict__ error_flag)
+{
+    const int64_t total = out_off[T_out] * units_per_pos;
+    constexpr int kPerThread = 8;
+    const int64_t chunk = 256 * kPerThread;
+    int64_t i = -1;
+    int64_t seg_hi = 0, delta = 0, group_lo = 0, group_hi = 0;
+    VT* dst = nullptr;
+    for (int64_t c0 = static_cast<int64_t>(blockIdx.x) * chunk; c0 < total; c0 += static_cast<int64_t>(gridDim.x) * chunk) {
+#pragma unroll 4
+        for (int j = 0; j < kPerThread; ++j) {
+            const int64_t u = c0 + j * 256 + threadIdx.x;
+            if (u >= total) break;
+            const int64_t o = u / units_per_pos;
+            if (i < 0 || o >= seg_hi) {
+                int64_t lo = (i < 0) ? 0 : i, hi = T_out;
+                while (hi - lo > 1) {
+                    const int64_t mid = (lo + hi) >> 1;
+                    if (out_off[mid] <= o) lo = mid; else hi = mid;
+                }
+                i = lo;
+                seg_hi = out_off[i + 1];
+                const int64_t p = permute[i];
+                delta = (((p >= 0 && p < T_in) ? in_off[p] : 0) - out_off[i]) * units_per_pos;
+                const int64_t g = i / tables_per_dest;
+                group_lo = out_off[g * tables_per_dest] * units_per_pos;
+                group_hi = group_lo + dest_capacity * units_per_pos;
+                dst = reinterpret_cast<VT*>(dest_bases[g]);
+            }
+            if (u < group_hi) dst[u - group_lo] = src[u + delta];
+            else if (error_flag) atomicOr(error_flag, 2);
+        }
+    }
+}
+
 template <typename VT>
 int launch_segments(const void* src, void* dst, int64_t units_per_pos, int64_t capacity, const int32_t* permute, int64_t T_in,
                     int64_t T_out, const int64_t* in_off, const int64_t* out_off, cudaStream_t s)
@@ -720,6 +764,47 @@ extern "C" int tbe_b200_permute_2d_sparse_copy(const int32_t* permute, int64_t T
     if (rc != TBE_B200_OK) return rc;
     if (weights) rc = copy_segments(weights, out_weights, weight_row_bytes, out_capacity, permute, T_in, T_out, in_off, out_off, s);
     return rc;
+}
+
+extern "C" int tbe_b200_permute_2d_sparse_copy_to_dests(const int32_t* permute, int64_t T_out, int64_t T_in, const void* values,
+                                                        int64_t value_bytes, const int64_t* dest_bases, int64_t tables_per_dest,
+                                                        int64_t dest_capacity, int64_t total_hint, const void* scratch, int32_t* error_flag,
+                                                        tbe_b200_stream_t stream)
+{
+    using namespace tbe;
+    if (T_in <= 0 || T_out <= 0) return fail(TBE_B200_ERR_INVALID_ARGUMENT, "permute_2d_sparse_copy_to_dests: T_in and T_out must be positive");
+    if (tables_per_dest <= 0 || T_out % tables_per_dest != 0)
+        return fail(TBE_B200_ERR_INVALID_ARGUMENT, "permute_2d_sparse_copy_to_dests: T_out (%lld) must be a multiple of tables_per_dest (%lld)",
+                    static_cast<long long>(T_out), static_cast<long long>(tables_per_dest));
+    if (dest_capacity < 0 || total_hint < 0) return fail(TBE_B200_ERR_INVALID_ARGUMENT, "permute_2d_sparse_copy_to_dests: negative size");
+    if (!permute || !scratch || !dest_bases) return fail(TBE_B200_ERR_INVALID_ARGUMENT, "permute_2d_sparse_copy_to_dests: a required pointer is NULL");
+    if (total_hint == 0) return TBE_B200_OK;
+    if (!values || value_bytes <= 0) return fail(TBE_B200_ERR_INVALID_ARGUMENT, "permute_2d_sparse_copy_to_dests: values are missing");
+    cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+    const int64_t* seg_len = static_cast<const int64_t*>(scratch);
+    const int64_t* in_off = seg_len + T_in;
+    const int64_t* out_off = in_off + T_in + 1;
+    // unit of the copy: the widest that divides a value and the source address (destinations are 16-byte aligned)
+    const uintptr_t a = reinterpret_cast<uintptr_t>(values);
+    int unit = 16;
+    while (unit > 1 && (value_bytes % unit != 0 || a % unit != 0)) unit >>= 1;
+    const int64_t upp = value_bytes / unit;
+    const int64_t units = total_hint * upp;
+    const int64_t want = (units + 256 * 8 - 1) / (256 * 8);
+    const int64_t cap = static_cast<int64_t>(sm_count()) * 32;
+    const unsigned blocks = static_cast<unsigned>(want < cap ? want : cap);
+#define TBE_TO_DESTS(VT)                                                                                                                      \
+    permute_segments_to_dests_kernel<VT><<<blocks, 256, 0, s>>>(static_cast<const VT*>(values), dest_bases, tables_per_dest, dest_capacity, upp, \
+                                                                permute, T_in, T_out, in_off, out_off, error_flag)
+    switch (unit) {
+        case 16: TBE_TO_DESTS(uint4); break;
+        case 8: TBE_TO_DESTS(uint64_t); break;
+        case 4: TBE_TO_DESTS(uint32_t); break;
+        case 2: TBE_TO_DESTS(uint16_t); break;
+        default: TBE_TO_DESTS(uint8_t); break;
+    }
+#undef TBE_TO_DESTS
+    return check_launch("permute_segments_to_dests_kernel");
 }
 
 // ---- complete cumsum for callers that must not allocate ---------------------------------------

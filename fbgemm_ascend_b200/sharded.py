@@ -251,11 +251,15 @@ class FeatureMajorInputDist:
 
     def __init__(self, plan: ShardPlan, group=None, device: Optional[torch.device] = None,
                  permute_fn: Optional[Callable] = None, cumsum_fn: Optional[Callable] = None,
-                 index_dtype: torch.dtype = torch.int64) -> None:
+                 index_dtype: torch.dtype = torch.int64, wire_dtype: Optional[torch.dtype] = None,
+                 exchange: str = "nccl", slot_capacity: int = 0, max_polls: int = 1 << 21) -> None:
         self.plan = plan
         self.group = group
         self.device = device if device is not None else torch.device("cpu")
-        self.index_dtype = index_dtype
+        self.index_dtype = index_dtype        # dtype of the indices and offsets handed to the lookup
+        self.wire_dtype = wire_dtype          # dtype of the indices while they are permuted and exchanged (None: as given);
+                                              # row numbers fit 31 bits, so int32 halves the bytes moved
+        self.stages: Optional[list] = None    # set to [] to have one call record (name, CUDA event) after every stage
         self.permute_fn = permute_fn or (lambda perm, lengths, values, weights, total:
                                          torch.ops.fbgemm.permute_2D_sparse_data(perm, lengths, values, weights, total))
         self.cumsum_fn = cumsum_fn or (lambda x: torch.ops.fbgemm.asynchronous_complete_cumsum(x))
@@ -266,13 +270,107 @@ class FeatureMajorInputDist:
         t32 = lambda v: torch.tensor(v, dtype=torch.int32, device=self.device)
         self.by_owner = t32(p.exchanged_order)                                            # step 1
         self.to_table_major = t32([s * self.T_loc + j for j in range(self.T_loc) for s in range(p.world)])   # step 3
+        # "direct": no index all-to-all -- the first permute stores every owner's values straight into a slot of that
+        # owner's receive buffer (peer memory, plain stores over NVLink), step flags say when a buffer is complete
+        self.exchange = exchange if p.world > 1 else "nccl"
+        if exchange not in ("nccl", "direct"):
+            raise ValueError(f"unknown exchange {exchange!r}")
+        self.max_polls = max_polls
+        if self.exchange == "direct":
+            if slot_capacity <= 0:
+                raise ValueError("exchange='direct' needs slot_capacity: the most indices one rank sends to one owner")
+            self._setup_direct(int(slot_capacity))
+
+    def _setup_direct(self, cap: int) -> None:
+        import torch.distributed._symmetric_memory as symm_mem
+        from . import cabi
+        p, w = self.plan, self.plan.world
+        wire = self.wire_dtype or self.index_dtype
+        esz = torch.empty((), dtype=wire).element_size()
+        agreed = torch.tensor([cap], dtype=torch.int64, device=self.device)
+        dist.all_reduce(agreed, op=dist.ReduceOp.MAX, group=self.group)      # every rank's buffer must have one size
+        cap = (int(agreed.item()) + 15) // 16 * 16          # slots stay 16-byte aligned for every element size
+        self.slot_capacity = cap
+        gname = self.group.group_name if self.group is not None else dist.group.WORLD.group_name
+        # receive buffer of this rank: [2 buffers][world slots][cap]; slot s is written by rank s alone
+        self._recv = symm_mem.empty((2, w, cap), dtype=wire, device=self.device)
+        hdl = symm_mem.rendezvous(self._recv, gname)
+        ptrs = [int(x) for x in hdl.buffer_ptrs]
+        self._dest_bases = [torch.tensor([q + (k * w + p.rank) * cap * esz for q in ptrs], dtype=torch.int64, device=self.device)
+                            for k in range(2)]
+        self._flags = symm_mem.empty((2, w), dtype=torch.int64, device=self.device)
+        self._flags.zero_()
+        fhdl = symm_mem.rendezvous(self._flags, gname)
+        self._flag_ptrs = [torch.tensor([q + k * w * 8 for q in fhdl.buffer_ptrs], dtype=torch.int64, device=self.device) for k in range(2)]
+        self._handles = (hdl, fhdl)
+        self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self._scratch = torch.empty(cabi.permute_2d_sparse_scratch_elems(len(p.dims), len(p.dims)), dtype=torch.int64, device=self.device)
+        # second permute over world x (T_loc + 1) segments: the extra one per source stands for the unused rest of its slot
+        t32 = lambda v: torch.tensor(v, dtype=torch.int32, device=self.device)
+        self._to_table_major_slots = t32([s * (self.T_loc + 1) + j for j in range(self.T_loc) for s in range(w)])
+        self._step = 0
+        torch.cuda.synchronize(self.device)
+        dist.barrier(group=self.group)
+
+    def check_status(self) -> int:
+        """0, or bit 2 (a slot was too small: values were dropped) / bit 16 (a peer's step flag did not arrive in time)."""
+        return int(self.status.item()) if self.exchange == "direct" else 0
+
+    def _call_direct(self, lengths, indices):
+        from . import cabi
+        p, w, T_loc, B_loc, cap = self.plan, self.plan.world, self.T_loc, self.plan.local_batch, self.slot_capacity
+        k = self._step & 1
+        self._step += 1
+        value = (self._step + 1) // 2
+        self._mark("start")
+        if self.wire_dtype is not None and indices.dtype != self.wire_dtype:
+            indices = indices.to(self.wire_dtype)
+            self._mark("narrow")
+        # 1. permute by owner, stored straight into slot `rank` of every owner's buffer k; then this rank's flag there
+        len_by_owner = cabi.permute_2d_sparse_offsets(self.by_owner, lengths.contiguous(), self._scratch, self.status)
+        cabi.permute_2d_sparse_copy_to_dests(self.by_owner, len(p.dims), indices.contiguous(), self._dest_bases[k], T_loc, cap, self._scratch,
+                                             self.status)
+        cabi.signal_peers(self._flag_ptrs[k], w, p.rank, value)
+        self._mark("permute_by_owner_into_peer_slots")
+        # 2. lengths: a small all-to-all; the host needs the number of values that arrive to size the result
+        len_recv = torch.empty_like(len_by_owner)
+        dist.all_to_all_single(len_recv.view(-1), len_by_owner.view(-1), group=self.group)
+        send_counts = len_by_owner.view(w, -1).sum(1, dtype=torch.int64)
+        recv_counts = len_recv.view(w, -1).sum(1, dtype=torch.int64)
+        self._mark("lengths_all_to_all")
+        counts = torch.stack([send_counts, recv_counts]).cpu()
+        if int(counts.max()) > cap:
+            raise ValueError(f"slot_capacity {cap} is too small: a rank sends or receives {int(counts.max())} values for one owner")
+        total = int(counts[1].sum())
+        self._mark("host_read_of_counts")
+        cabi.wait_flags(self._flags[k], w, value, self.max_polls, self.status)
+        self._mark("wait_for_peer_stores")
+        # 3. slots -> table-major: every source's slot is its T_loc segments plus one segment of unused space
+        len_ext = torch.zeros((w, T_loc + 1, B_loc), dtype=len_recv.dtype, device=self.device)
+        len_ext[:, :T_loc] = len_recv.view(w, T_loc, B_loc)
+        len_ext[:, T_loc, 0] = cap - recv_counts
+        len_tm, idx_tm, _ = self.permute_fn(self._to_table_major_slots, len_ext.view(w * (T_loc + 1), B_loc), self._recv[k].view(-1), None, total)
+        self._mark("permute_to_table_major")
+        offsets = self.cumsum_fn(len_tm.reshape(-1)).to(self.index_dtype)
+        idx_tm = idx_tm.to(self.index_dtype)
+        self._mark("cumsum")
+        return idx_tm, offsets, None
 
     def __call__(self, lengths: torch.Tensor, indices: torch.Tensor, weights: Optional[torch.Tensor] = None):
         p, w, T_loc, B_loc = self.plan, self.plan.world, self.T_loc, self.plan.local_batch
         if tuple(lengths.shape) != (len(p.dims), B_loc):
             raise ValueError(f"lengths must be [{len(p.dims)}, {B_loc}], got {tuple(lengths.shape)}")
+        if self.exchange == "direct":
+            if weights is not None:
+                raise NotImplementedError("exchange='direct' moves indices only; use exchange='nccl' for per-sample weights")
+            return self._call_direct(lengths, indices)
+        self._mark("start")
+        if self.wire_dtype is not None and indices.dtype != self.wire_dtype:
+            indices = indices.to(self.wire_dtype)
+            self._mark("narrow")
         # 1. tables grouped by owner: owner r's tables are rows [r * T_loc, (r + 1) * T_loc) of the result
         len_by_owner, idx_by_owner, w_by_owner = self.permute_fn(self.by_owner, lengths, indices, weights, indices.numel())
+        self._mark("permute_by_owner")
         # 2. exchange
         send_counts = len_by_owner.view(w, -1).sum(1, dtype=torch.int64)
         if w == 1:
@@ -282,16 +380,34 @@ class FeatureMajorInputDist:
             len_recv = torch.empty_like(len_by_owner)
             dist.all_to_all_single(len_recv.view(-1), len_by_owner.contiguous().view(-1), group=self.group)
             recv_counts = len_recv.view(w, -1).sum(1, dtype=torch.int64)
+            self._mark("lengths_all_to_all")
             counts = torch.stack([send_counts, recv_counts]).cpu()                        # the one host read of the step
             send_l, recv_l = counts[0].tolist(), counts[1].tolist()
             total = int(sum(recv_l))
+            self._mark("host_read_of_split_sizes")
             idx_recv = torch.empty(total, dtype=indices.dtype, device=indices.device)
             dist.all_to_all_single(idx_recv, idx_by_owner.contiguous(), recv_l, send_l, group=self.group)
+            self._mark("indices_all_to_all")
             w_recv = None
             if weights is not None:
                 w_recv = torch.empty(total, dtype=weights.dtype, device=weights.device)
                 dist.all_to_all_single(w_recv, w_by_owner.contiguous(), recv_l, send_l, group=self.group)
         # 3. (source rank, local table, sample) -> (local table, source rank, sample) = table-major over the global batch
         len_tm, idx_tm, w_tm = self.permute_fn(self.to_table_major, len_recv.view(w * T_loc, B_loc), idx_recv, w_recv, total)
+        self._mark("permute_to_table_major")
         offsets = self.cumsum_fn(len_tm.reshape(-1)).to(self.index_dtype)
-        return idx_tm.to(self.index_dtype), offsets, w_tm
+        idx_tm = idx_tm.to(self.index_dtype)
+        self._mark("cumsum")
+        return idx_tm, offsets, w_tm
+
+    def _mark(self, name: str) -> None:
+        if self.stages is not None and self.device.type == "cuda":
+            e = torch.cuda.Event(enable_timing=True)
+            e.record()
+            self.stages.append((name, e))
+
+    def stage_ms(self) -> dict:
+        """Milliseconds between consecutive marks of the recorded call (device time on the current stream)."""
+        torch.cuda.synchronize()
+        st = self.stages or []
+        return {st[i][0]: round(st[i - 1][1].elapsed_time(st[i][1]), 4) for i in range(1, len(st))}

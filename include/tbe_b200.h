@@ -236,6 +236,20 @@ int tbe_b200_permute_2d_sparse_copy(const int32_t* permute, int64_t T_out, int64
                                     void* out_weights, int64_t out_capacity, const void* scratch,
                                     tbe_b200_stream_t stream);
 
+/* The copy step with several output buffers (no counterpart in the reference, which has no multi-device code): output
+ * table i belongs to destination i / tables_per_dest, and the values of a destination's tables land one after the
+ * other from dest_bases[destination] on.  dest_bases is a device array of T_out / tables_per_dest addresses, each
+ * 16-byte aligned and writable from this GPU -- local memory or a peer's (the stores then cross NVLink; this is how
+ * the index all-to-all in front of a table-wise sharded lookup is folded into the permute).  A destination takes at
+ * most dest_capacity values; values beyond are dropped and bit 2 is or'ed into *error_flag (if given).  total_hint
+ * is an upper bound of the number of values (it sizes the grid; the input size will do).  `scratch` is what
+ * tbe_b200_permute_2d_sparse_offsets left.  Completion at a peer is the caller's business
+ * (tbe_b200_signal_peers / tbe_b200_wait_flags on the same stream). */
+int tbe_b200_permute_2d_sparse_copy_to_dests(const int32_t* permute, int64_t T_out, int64_t T_in, const void* values,
+                                             int64_t value_bytes, const int64_t* dest_bases, int64_t tables_per_dest,
+                                             int64_t dest_capacity, int64_t total_hint, const void* scratch,
+                                             int32_t* error_flag, tbe_b200_stream_t stream);
+
 /* ---- step flags of a table-wise sharded lookup (one process per GPU) ---------------------------- */
 
 /* A rank tells its peers that the pooled rows it stored into their output buffers for step `value` are in place:

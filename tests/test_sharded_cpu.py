@@ -138,7 +138,7 @@ def _local_request(c, rank, world):
     return np.ascontiguousarray(l_loc), idx
 
 
-def _dist_main(rank, world, port, weighted, q):
+def _dist_main(rank, world, port, weighted, q, narrow=False):
     try:
         os.environ["MASTER_ADDR"] = "127.0.0.1"
         os.environ["MASTER_PORT"] = str(port)
@@ -154,8 +154,9 @@ def _dist_main(rank, world, port, weighted, q):
             assert v.size == total
             return torch.from_numpy(l), torch.from_numpy(v), None if w is None else torch.from_numpy(w)
 
+        kw = dict(wire_dtype=torch.int32, index_dtype=torch.int32) if narrow else {}
         ind = FeatureMajorInputDist(plan, group=None, device=torch.device("cpu"), permute_fn=permute_fn,
-                                    cumsum_fn=lambda x: torch.from_numpy(O.complete_cumsum(x.numpy())))
+                                    cumsum_fn=lambda x: torch.from_numpy(O.complete_cumsum(x.numpy())), **kw)
         l_loc, idx_loc = _local_request(c, rank, world)
         wts = None
         if weighted:
@@ -167,6 +168,8 @@ def _dist_main(rank, world, port, weighted, q):
         want_len = np.concatenate([np.diff(offs[t * B:(t + 1) * B + 1]) for t in plan.local_tables])
         want_off = np.concatenate([[0], np.cumsum(want_len)])
         ok = np.array_equal(idx_tm.numpy(), want_idx) and np.array_equal(offs_tm.numpy(), want_off)
+        if narrow:
+            ok = ok and idx_tm.dtype == torch.int32 and offs_tm.dtype == torch.int32
         if weighted:
             Bl = B // world
             src = np.concatenate([np.repeat(np.arange(B) // Bl, np.diff(offs[t * B:(t + 1) * B + 1])) for t in plan.local_tables])
@@ -177,14 +180,15 @@ def _dist_main(rank, world, port, weighted, q):
         q.put((rank, False, f"{type(e).__name__}: {e}\n{traceback.format_exc()[-800:]}"))
 
 
-@pytest.mark.parametrize("weighted", [False, True])
-def test_feature_major_input_dist_two_ranks(weighted):
+@pytest.mark.parametrize("weighted,narrow", [(False, False), (True, False), (False, True)])
+def test_feature_major_input_dist_two_ranks(weighted, narrow):
     """Index all-to-all in front of the lookup: two CPU ranks, each with the feature-major request of its own
-    samples, end up with the table-major request of the global batch for their own tables."""
+    samples, end up with the table-major request of the global batch for their own tables (also with the indices
+    narrowed to int32 for the permutes and the exchange)."""
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_dist_main, args=(r, 2, port, weighted, q)) for r in range(2)]
+    procs = [ctx.Process(target=_dist_main, args=(r, 2, port, weighted, q, narrow)) for r in range(2)]
     for pr in procs:
         pr.start()
     res = sorted(q.get(timeout=120) for _ in range(2))

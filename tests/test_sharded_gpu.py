@@ -85,6 +85,22 @@ def _rank_main(rank, world, port, q):
         ind = FeatureMajorInputDist(plan, group=dist.group.WORLD, device=dev)
         idx_tm, offs_tm, _ = ind(torch.stack(lens_fm), torch.cat(idx_fm))
         ok["input_dist"] = bool(torch.equal(idx_tm, batch.indices) and torch.equal(offs_tm, batch.offsets))
+        if world > 1:
+            # the same with the exchange folded into the first permute (peer stores into per-source slots + step flags),
+            # several steps so that both buffers are used twice; then with the indices narrowed to int32 on the way
+            lens_all, idx_all = torch.stack(lens_fm), torch.cat(idx_fm)
+            cap = int(idx_all.numel())
+            ind_d = FeatureMajorInputDist(plan, group=dist.group.WORLD, device=dev, exchange="direct", slot_capacity=cap)
+            good = True
+            for _ in range(4):
+                i_d, o_d, _ = ind_d(lens_all, idx_all)
+                good = good and bool(torch.equal(i_d, batch.indices) and torch.equal(o_d, batch.offsets))
+            ind_32 = FeatureMajorInputDist(plan, group=dist.group.WORLD, device=dev, exchange="direct", slot_capacity=cap,
+                                           wire_dtype=torch.int32, index_dtype=torch.int32)
+            for _ in range(3):
+                i_d, o_d, _ = ind_32(lens_all, idx_all)
+                good = good and bool(torch.equal(i_d, batch.indices.to(torch.int32)) and torch.equal(o_d, batch.offsets.to(torch.int32)))
+            ok["input_dist_direct"] = good and ind_d.check_status() == 0 and ind_32.check_status() == 0
         q.put((rank, ok, ""))
         dist.barrier()
         dist.destroy_process_group()
@@ -118,7 +134,7 @@ def test_two_ranks_both_paths_bit_exact():
     res = _run(2)
     for rank, ok, err in res:
         assert err == "", err
-        assert ok == {"nccl": True, "direct": True, "status": 0, "oracle": True, "input_dist": True}, res
+        assert ok == {"nccl": True, "direct": True, "status": 0, "oracle": True, "input_dist": True, "input_dist_direct": True}, res
 
 
 def test_wait_for_step_flags_is_bounded():

@@ -127,6 +127,48 @@ def test_cumsum_tile_whose_wait_runs_out_adds_up_its_prefix_itself():
     assert r.returncode == 0 and "alone-ok" in r.stdout, r.stdout[-500:] + r.stderr[-1500:]
 
 
+@pytest.mark.gpu
+@pytest.mark.parametrize("vname", ["int64", "int32", "float16"])
+def test_permute_copy_to_several_destinations(vname):
+    """The copy step with one output buffer per group of output tables (what folds the index all-to-all into the
+    permute): every buffer holds its group's part of the plain permute's result, nothing is written behind it, and a
+    buffer that is too small takes what fits and reports bit 2."""
+    import torch
+    import fbgemm_ascend_b200  # noqa: F401
+    from fbgemm_ascend_b200 import cabi
+
+    rng = _rng("to-dests", vname)
+    T_in, groups, tpd, B = 12, 3, 4, 50
+    permute = rng.permutation(T_in).astype(np.int32)
+    lengths = rng.integers(0, 10, (T_in, B)).astype(np.int64)
+    total = int(lengths.sum())
+    vdt = _torch_dtype(vname)
+    values = torch.arange(total, dtype=torch.float32).to(vdt) if vdt.is_floating_point else torch.arange(total, dtype=vdt)
+    want_len, want_val, _ = O.permute_2d_sparse_data(permute, lengths, _as_np(values), None)
+    seg = want_len.sum(1)
+    bounds = np.concatenate([[0], np.cumsum(seg)])
+    dev = torch.device("cuda")
+    perm_d, len_d, val_d = torch.from_numpy(permute).to(dev), torch.from_numpy(lengths).to(dev), values.to(dev)
+    scratch = torch.empty(cabi.permute_2d_sparse_scratch_elems(T_in, T_in), dtype=torch.int64, device=dev)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    out_len = cabi.permute_2d_sparse_offsets(perm_d, len_d, scratch, status)
+    assert np.array_equal(out_len.cpu().numpy(), want_len)
+    group_sizes = [int(bounds[(g + 1) * tpd] - bounds[g * tpd]) for g in range(groups)]
+    for cap, overflow in ((max(group_sizes) + 8, False), (min(group_sizes) // 2, True)):
+        pad = 64
+        bufs = [torch.full((cap + pad,), 7, dtype=vdt, device=dev) for _ in range(groups)]
+        bases = torch.tensor([b.data_ptr() for b in bufs], dtype=torch.int64, device=dev)
+        status.zero_()
+        cabi.permute_2d_sparse_copy_to_dests(perm_d, T_in, val_d, bases, tpd, cap, scratch, status)
+        torch.cuda.synchronize()
+        assert int(status.item()) == (2 if overflow else 0)
+        for g in range(groups):
+            part = want_val[bounds[g * tpd]:bounds[(g + 1) * tpd]][:cap]
+            got = _as_np(bufs[g].cpu())
+            assert np.array_equal(got[:part.size], part), (g, cap)
+            assert np.all(got[part.size:] == _as_np(torch.full((1,), 7, dtype=vdt))[0]), (g, cap)
+
+
 VTYPES = ["int64", "int32", "float32", "float16", "bfloat16"]
 WTYPES = [None, "float32", "float16", "bfloat16", "float64", "int32", "int64"]
 
