@@ -1100,14 +1100,8 @@ __device__ __noinline__ void pool_run_stream(const LookupParams& p, const TableM
             }
             if (bag_start < lo) write_partial();
             else store_bag(cur, bag_end - bag_start);
-#if defined(TBE_EXP_NOZERO)
-#elif defined(TBE_EXP_MULZERO)
-#pragma unroll
-            for (int s = 0; s < EPL; ++s) acc[s] *= 0.0f;
-#else
 #pragma unroll
             for (int s = 0; s < EPL; ++s) acc[s] = 0.0f;
-#endif
             bias_acc = 0.0f;
             ++cur;
             bag_start = bag_end;
@@ -1325,25 +1319,6 @@ __device__ __forceinline__ void pool_run_stream_by_width(const LookupParams& p, 
     else pool_run_stream<TY, 32, 16, WEIGHTED, FOLD>(p, m, i0, nb, b, lane, wsm);
 }
 
-#ifdef TBE_STREAM_BENCH_SHAPES_ONLY
-// Experiment builds: only the unweighted INT8 D = 128 16-bit-output stream and the unweighted INT4 streams are compiled;
-// everything else must not be run.
-template <bool WEIGHTED>
-__device__ __forceinline__ void pool_run_stream_by_type(const LookupParams& p, const TableMeta& m, int64_t i0, int nb, int64_t b,
-                                                        int lane, uint32_t wsm)
-{
-    if constexpr (!WEIGHTED) {
-        if (m.ty == TBE_B200_INT4) pool_run_stream_by_width<TBE_B200_INT4, false, false>(p, m, i0, nb, b, lane, wsm);
-        if (m.ty == TBE_B200_INT8 && p.out_ty != TBE_B200_FP32 && m.D == 128) {
-#ifdef TBE_BENCH_EPL16
-            pool_run_stream<TBE_B200_INT8, 8, 16, false, true>(p, m, i0, nb, b, lane, wsm);
-#else
-            pool_run_stream<TBE_B200_INT8, 4, 32, false, true>(p, m, i0, nb, b, lane, wsm);
-#endif
-        }
-    }
-}
-#else
 template <bool WEIGHTED>
 __device__ __forceinline__ void pool_run_stream_by_type(const LookupParams& p, const TableMeta& m, int64_t i0, int nb, int64_t b,
                                                         int lane, uint32_t wsm)
@@ -1364,7 +1339,6 @@ __device__ __forceinline__ void pool_run_stream_by_type(const LookupParams& p, c
         default: pool_run_stream_by_width<TBE_B200_FP32, WEIGHTED, false>(p, m, i0, nb, b, lane, wsm); return;
     }
 }
-#endif
 
 
 // A run of bags of one table through the general per-bag code.
@@ -1580,6 +1554,7 @@ __device__ __forceinline__ void nobag_rows(const LookupParams& p, const TableMet
     const bool active = k < nunits;
     const int esz = (p.out_ty == TBE_B200_FP32) ? 4 : 2;
     const int row_out_bytes = D * esz, pieces_per_row = row_out_bytes / 16;
+    const int piece_shift = (pieces_per_row & (pieces_per_row - 1)) == 0 ? __ffs(pieces_per_row) - 1 : -1;   // power of two: no division
     const bool staged = (reinterpret_cast<uintptr_t>(p.output) & 15) == 0 && (p.out_stride * esz) % 16 == 0;   // warp-uniform
     // The warp's positions are narrowed and checked once (lane l holds positions l and l + 32), then taken U steps of
     // G rows at a time: the row loads of all U steps are issued before the first row is decoded, so U * G rows per warp
@@ -1689,7 +1664,7 @@ __device__ __forceinline__ void nobag_rows(const LookupParams& p, const TableMet
             }
             __syncwarp();
             for (int c = lane; c < G * pieces_per_row; c += kWarp) {
-                const int row = c / pieces_per_row, piece = c - row * pieces_per_row;
+                const int row = piece_shift >= 0 ? (c >> piece_shift) : c / pieces_per_row, piece = c - row * pieces_per_row;
                 const int rpos = r0 + u * G + row;
                 if (rpos < cnt)
                     st_stream16(static_cast<char*>(p.output) + (n + rpos) * p.out_stride * esz + 16 * piece,
