@@ -300,6 +300,28 @@ def test_scatter_with_rows_that_are_not_16_byte_aligned(out_dtype):
     got = torch.cat(parts, 0)[:B].float().cpu().numpy()
     assert_close(got, want, out_ty, "misaligned scatter")
 
+@pytest.mark.parametrize("index_dtype", [np.int32, np.int64])
+@pytest.mark.parametrize("weighted", [False, True])
+def test_one_wave_launch_with_ragged_bags(index_dtype, weighted):
+    """A launch that fills the GPU about once (12 000 bags, 400 000 rows: every warp takes a handful of bags) with bags
+    as unequal as they get: empty bags at the very start and end and in long stretches, one bag of 5000 rows, stretches
+    of one-row bags, three table types and widths."""
+    rng = np.random.default_rng(seed_of("one-wave", index_dtype.__name__, weighted))
+    T, B = 3, 4000
+    lens = rng.poisson(33, T * B).astype(np.int64)
+    lens[:200] = 0
+    lens[-300:] = 0
+    lens[5000:5600] = 0
+    lens[2000:2600] = 1
+    lens[7000] = 5000
+    lens[7001:7040] = 0
+    lens[9000:9010] = 700
+    c = make_case(rng, [O.INT8, O.INT4, O.FP16], [128, 64, 32], [5000, 3000, 2000], B, lens, index_dtype, weighted, prune_frac=0.01)
+    assert c.indices.size > 350_000
+    for pooling, out_ty in ((O.SUM, O.FP16), (O.MEAN, O.FP32)):
+        run(c, pooling, out_ty, f"one wave, ragged bags, {index_dtype.__name__}")
+
+
 
 @pytest.mark.parametrize("weights_ty", [O.INT8, O.INT4, O.FP16, O.FP8, O.FP32])
 @pytest.mark.parametrize("D", [64, 128, 256, 512])
