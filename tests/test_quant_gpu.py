@@ -77,7 +77,8 @@ def test_half_variants():
 
 
 @pytest.mark.parametrize("bit_rate", [4, 2])
-@pytest.mark.parametrize("shape", [(2000, 128), (500, 64), (300, 8), (10, 16), (100, 256), (7, 4096), (64, 24)])
+@pytest.mark.parametrize("shape", [(2000, 128), (500, 64), (300, 8), (10, 16), (100, 256), (7, 4096), (64, 24), (77, 32), (1001, 96),
+                                   (33, 160), (5, 128), (1, 256)])
 @pytest.mark.parametrize("kind", KINDS)
 def test_quantize_nbit_bit_exact(bit_rate, shape, kind):
     import fbgemm_ascend_b200  # noqa: F401
@@ -93,7 +94,7 @@ def test_quantize_nbit_bit_exact(bit_rate, shape, kind):
 
 
 @pytest.mark.parametrize("ty", [O.INT8, O.INT4, O.INT2, O.FP16])
-@pytest.mark.parametrize("shape", [(1000, 128), (333, 64), (50, 16), (20, 1024)])
+@pytest.mark.parametrize("shape", [(1000, 128), (333, 64), (50, 16), (20, 1024), (101, 96), (9, 256), (45, 32)])
 @pytest.mark.parametrize("row_alignment", [16, 1])
 def test_table_rows_bit_exact(ty, shape, row_alignment):
     """Direct fp32 -> table rows equals oracle quantize + pack; and so does quantize then pack on the GPU."""
