@@ -247,6 +247,16 @@ class FeatureMajorInputDist:
 
     The three operators are the package's own (``torch.ops.fbgemm.*``) unless replaced through the hooks, which
     lets the plumbing run on CPU ranks (gloo) in the tests.
+
+    ``exchange="direct"`` (GPUs of one box, symmetric memory) replaces step 2's index all-to-all: the permute of step 1
+    stores owner ``r``'s values straight into slot ``rank`` of ``r``'s receive buffer (``world`` slots of
+    ``slot_capacity`` entries, double-buffered; plain peer stores, no multicast), raises its step flag at every peer
+    and waits -- bounded, ``max_polls`` -- for theirs; step 3 reads the slots in place, the unused rest of every slot
+    being one more segment that its permute list leaves out.  Only the lengths still go through a (small) collective.
+    Per-sample weights are not moved on this path.  A slot that is too small drops values and sets bit 2 of ``status``;
+    the ranks that see the count on the host (the sender and the owner) raise ``ValueError`` after the step, the others
+    find out at their next collective.  ``wire_dtype=torch.int32`` narrows the indices before they are permuted and
+    exchanged (row numbers fit 31 bits), on either path.
     """
 
     def __init__(self, plan: ShardPlan, group=None, device: Optional[torch.device] = None,
