@@ -1402,15 +1402,22 @@ __device__ __forceinline__ void pool_run_general(const LookupParams& p, const Ta
 
 // ---- kernels -----------------------------------------------------------------
 
-constexpr int kWarpsPerBlock = 4;
+// Warps per block.  With 8 (two blocks per SM) or 16 (one) the warps of an SM work on fewer tables at a time, which
+// helps launches whose tables differ in type or width (their loops compete for the instruction cache): measured
+// +4.5 % / +2.7 % on benchmark configuration 3 and +1.6 % / +0.4 % on configuration 5, but -0.9 % / -4.6 % on the
+// single-shape configuration 4 (a finished block leaves its SM emptier for longer), so 4 it is.
+#ifndef TBE_WARPS_PER_BLOCK
+#define TBE_WARPS_PER_BLOCK 4
+#endif
+constexpr int kWarpsPerBlock = TBE_WARPS_PER_BLOCK;
 #ifndef TBE_SPAN_LARGE
 #define TBE_SPAN_LARGE 31
 #endif
 #ifndef TBE_STREAM_BLOCKS_PER_SM
-#define TBE_STREAM_BLOCKS_PER_SM 4   // 16 resident warps per SM at up to 128 registers (32 accumulators per lane); measured best
+#define TBE_STREAM_BLOCKS_PER_SM (16 / TBE_WARPS_PER_BLOCK)   // 16 resident warps per SM at up to 128 registers (32 accumulators per lane); measured best
 #endif
 constexpr int kStreamBlocksPerSM = TBE_STREAM_BLOCKS_PER_SM;
-constexpr int kWideBlocksPerSM = 8;
+constexpr int kWideBlocksPerSM = 32 / TBE_WARPS_PER_BLOCK;
 
 // The T*B bags (bag i = t*B + b) are cut into spans of `span` consecutive bags, one span per warp, so a
 // warp walks `offsets`, `indices` and the per-sample weights front to back.  A span is processed as runs
@@ -1426,7 +1433,7 @@ __global__ void __launch_bounds__(kWarpsPerBlock* kWarp, WIDE ? kWideBlocksPerSM
 tbe_pooled_kernel(const __grid_constant__ LookupParams p)
 {
     constexpr int kSmemPerWarp = WIDE ? kWarpSmemBytes : kStreamSmemBytes;
-    __shared__ __align__(128) uint8_t smem[kWarpsPerBlock * kSmemPerWarp];
+    extern __shared__ __align__(128) uint8_t smem[];      // kWarpsPerBlock * kSmemPerWarp bytes, given at launch
     const int lane = threadIdx.x & 31;
     const int warp = threadIdx.x >> 5;
     const uint32_t wsm = smem_u32(smem) + warp * kSmemPerWarp;
@@ -1759,7 +1766,7 @@ constexpr int kSpanLarge = TBE_SPAN_LARGE;   // bags per warp when there is plen
 
 // Blocks of a kernel that fit on one SM of the current device (occupancy query, once per device and kernel).
 template <typename Kernel>
-int resident_blocks(Kernel kernel, int variant, int fallback)
+int resident_blocks(Kernel kernel, int variant, int fallback, int smem_bytes = 0)
 {
     constexpr int kMaxDev = 64, kVariants = 4;
     static std::atomic<int> cached[kMaxDev][kVariants];
@@ -1767,7 +1774,8 @@ int resident_blocks(Kernel kernel, int variant, int fallback)
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDev) return fallback;
     int n = cached[dev][variant].load(std::memory_order_relaxed);
     if (n == 0) {
-        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, kWarpsPerBlock * kWarp, 0) != cudaSuccess || n <= 0) {
+        if (smem_bytes > 48 * 1024) (void)cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, kWarpsPerBlock * kWarp, smem_bytes) != cudaSuccess || n <= 0) {
             (void)cudaGetLastError();
             n = fallback;
         }
@@ -1823,8 +1831,9 @@ int forced_span()
 template <typename IdxT, bool WIDE>
 int launch_pooled(LookupParams p, cudaStream_t s)
 {
+    constexpr int kSmemBytes = kWarpsPerBlock * (WIDE ? kWarpSmemBytes : kStreamSmemBytes);
     const int resident = resident_blocks(tbe_pooled_kernel<IdxT, WIDE>, (sizeof(IdxT) == 8 ? 2 : 0) + (WIDE ? 1 : 0),
-                                         WIDE ? kWideBlocksPerSM : kStreamBlocksPerSM);
+                                         WIDE ? kWideBlocksPerSM : kStreamBlocksPerSM, kSmemBytes);
     // Plenty of bags: fixed spans, as many blocks as that takes; the hardware block scheduler evens out the load.
     // Otherwise the spans are sized so that the warps fill a whole number of waves of resident warps.
     const int64_t slots = static_cast<int64_t>(sm_count()) * resident * kWarpsPerBlock;
@@ -1840,7 +1849,7 @@ int launch_pooled(LookupParams p, cudaStream_t s)
     const int64_t warps = (p.num_bags + p.span - 1) / p.span;
     const int64_t blocks = (warps + kWarpsPerBlock - 1) / kWarpsPerBlock;
     if (blocks > 0x7fffffffll) return fail(TBE_B200_ERR_UNSUPPORTED, "lookup: too many bags for one launch");
-    tbe_pooled_kernel<IdxT, WIDE><<<static_cast<unsigned>(blocks), kWarpsPerBlock * kWarp, 0, s>>>(p);
+    tbe_pooled_kernel<IdxT, WIDE><<<static_cast<unsigned>(blocks), kWarpsPerBlock * kWarp, kSmemBytes, s>>>(p);
     return check_launch("tbe_pooled_kernel");
 }
 
