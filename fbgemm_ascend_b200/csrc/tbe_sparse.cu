@@ -165,7 +165,10 @@ __global__ void __launch_bounds__(kScanThreads) scan_tiles_kernel(const T* __res
 // its shared memory for load + look-back (two to three L2 round trips under load) + copy-out, about 14 us, and
 // 3 x 64 KB per SM held that long is 4 TB/s.  Variants measured: 4096-element tiles in registers, 32 descriptors per
 // poll 165 us, 128 per poll 91 us (both bound by the chain of look-backs); 32 KB tiles, 6 blocks per SM, 256 per poll
-// 83 us; persistent blocks striding over the tiles 79-89 us.
+// 83 us; persistent blocks striding over the tiles 79-89 us; one block per SM walking its tiles through three buffers
+// (tile i + 1 arriving, tile i scanned, tile i - 1 written out behind the prefix found for it meanwhile, so that neither
+// the load nor the look-back holds the block up) 87 us / 312 us at 64 M: the blocks then run in lockstep, and every
+// round waits for the slowest block's sum.
 constexpr int kBigWorkers = 256;                          // threads that move and scan data
 constexpr int kBigThreads = kBigWorkers + 32;             // + one warp that only looks back
 constexpr int kBigChunks = 4096;                          // 16-byte chunks per tile
