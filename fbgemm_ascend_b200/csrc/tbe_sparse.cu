@@ -565,6 +565,79 @@ __global__ void __launch_bounds__(256) permute_segments_to_dests_kernel(const VT
     }
 }
 
+// The same for plain 4- and 8-byte values, two at a time: a thread takes a PAIR of consecutive positions of a
+// destination, counted from the destination's start, so that its store is one aligned 8- or 16-byte piece whatever the
+// parity of the segment starts (remote stores of twice the width load NVLink half as often); the two values are
+// fetched separately, since their sources need not be adjacent (a pair may straddle two tables) nor aligned.
+constexpr int kMaxPairDests = 64;
+template <typename VT, typename VT2>
+__global__ void __launch_bounds__(256) permute_pairs_to_dests_kernel(const VT* __restrict__ src, const int64_t* __restrict__ dest_bases,
+                                                                     int64_t tables_per_dest, int64_t dest_capacity, int n_dest,
+                                                                     const int32_t* __restrict__ permute, int64_t T_in, int64_t T_out,
+                                                                     const int64_t* __restrict__ in_off, const int64_t* __restrict__ out_off,
+                                                                     int32_t* __restrict__ error_flag)
+{
+    __shared__ int64_t pair_start[kMaxPairDests + 1];   // pairs in front of every destination
+    __shared__ int64_t group_lo[kMaxPairDests];          // first output position of every destination
+    __shared__ int64_t group_n[kMaxPairDests];           // positions it takes (at most dest_capacity)
+    if (threadIdx.x == 0) {
+        int64_t pairs = 0;
+        for (int g = 0; g < n_dest; ++g) {
+            const int64_t lo = out_off[g * tables_per_dest];
+            int64_t cnt = out_off[(g + 1) * tables_per_dest] - lo;
+            if (cnt > dest_capacity) {
+                cnt = dest_capacity;
+                if (error_flag && blockIdx.x == 0) atomicOr(error_flag, 2);
+            }
+            group_lo[g] = lo;
+            group_n[g] = cnt;
+            pair_start[g] = pairs;
+            pairs += (cnt + 1) >> 1;
+        }
+        pair_start[n_dest] = pairs;
+    }
+    __syncthreads();
+    const int64_t total_pairs = pair_start[n_dest];
+    constexpr int kPerThread = 4;
+    const int64_t chunk = 256 * kPerThread;
+    int g = 0;
+    int64_t i = -1, seg_hi = 0, delta = 0;
+    auto find_table = [&](int64_t o) {
+        // largest i with out_off[i] <= o; positions only grow, so the search starts at the current table
+        int64_t lo = (i < 0) ? 0 : i, hi = T_out;
+        while (hi - lo > 1) {
+            const int64_t mid = (lo + hi) >> 1;
+            if (out_off[mid] <= o) lo = mid; else hi = mid;
+        }
+        i = lo;
+        seg_hi = out_off[i + 1];
+        const int64_t p = permute[i];
+        delta = ((p >= 0 && p < T_in) ? in_off[p] : 0) - out_off[i];
+    };
+    for (int64_t c0 = static_cast<int64_t>(blockIdx.x) * chunk; c0 < total_pairs; c0 += static_cast<int64_t>(gridDim.x) * chunk) {
+#pragma unroll 2
+        for (int j = 0; j < kPerThread; ++j) {
+            const int64_t P = c0 + j * 256 + threadIdx.x;
+            if (P >= total_pairs) break;
+            while (P >= pair_start[g + 1]) ++g;
+            const int64_t rel = (P - pair_start[g]) << 1;
+            const int64_t u = group_lo[g] + rel;
+            if (i < 0 || u >= seg_hi) find_table(u);
+            const VT v0 = src[u + delta];
+            VT* dst = reinterpret_cast<VT*>(dest_bases[g]) + rel;
+            if (rel + 1 < group_n[g]) {
+                if (u + 1 >= seg_hi) find_table(u + 1);
+                VT2 both;
+                both.x = v0;
+                both.y = src[u + 1 + delta];
+                *reinterpret_cast<VT2*>(dst) = both;
+            } else {
+                *dst = v0;
+            }
+        }
+    }
+}
+
 template <typename VT>
 int launch_segments(const void* src, void* dst, int64_t units_per_pos, int64_t capacity, const int32_t* permute, int64_t T_in,
                     int64_t T_out, const int64_t* in_off, const int64_t* out_off, cudaStream_t s)
@@ -796,6 +869,21 @@ extern "C" int tbe_b200_permute_2d_sparse_copy_to_dests(const int32_t* permute, 
     const int64_t want = (units + 256 * 8 - 1) / (256 * 8);
     const int64_t cap = static_cast<int64_t>(sm_count()) * 32;
     const unsigned blocks = static_cast<unsigned>(want < cap ? want : cap);
+    const int64_t n_dest = T_out / tables_per_dest;
+    if ((value_bytes == 8 || value_bytes == 4) && a % value_bytes == 0 && n_dest <= kMaxPairDests) {
+        const int64_t pairs = (total_hint + 1) / 2 + n_dest;
+        const int64_t want2 = (pairs + 256 * 4 - 1) / (256 * 4);
+        const unsigned blocks2 = static_cast<unsigned>(want2 < cap ? want2 : cap);
+        if (value_bytes == 8)
+            permute_pairs_to_dests_kernel<unsigned long long, ulonglong2><<<blocks2, 256, 0, s>>>(
+                static_cast<const unsigned long long*>(values), dest_bases, tables_per_dest, dest_capacity, static_cast<int>(n_dest), permute, T_in,
+                T_out, in_off, out_off, error_flag);
+        else
+            permute_pairs_to_dests_kernel<uint32_t, uint2><<<blocks2, 256, 0, s>>>(static_cast<const uint32_t*>(values), dest_bases, tables_per_dest,
+                                                                                 dest_capacity, static_cast<int>(n_dest), permute, T_in, T_out, in_off,
+                                                                                 out_off, error_flag);
+        return check_launch("permute_pairs_to_dests_kernel");
+    }
 #define TBE_TO_DESTS(VT)                                                                                                                      \
     permute_segments_to_dests_kernel<VT><<<blocks, 256, 0, s>>>(static_cast<const VT*>(values), dest_bases, tables_per_dest, dest_capacity, upp, \
                                                                 permute, T_in, T_out, in_off, out_off, error_flag)

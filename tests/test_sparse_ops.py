@@ -137,10 +137,18 @@ def test_permute_copy_to_several_destinations(vname):
     import fbgemm_ascend_b200  # noqa: F401
     from fbgemm_ascend_b200 import cabi
 
-    rng = _rng("to-dests", vname)
-    T_in, groups, tpd, B = 12, 3, 4, 50
+    for T_in, groups, tpd, B, empty in ((12, 3, 4, 50, ()), (8, 8, 1, 7, (0, 3, 7)), (6, 2, 3, 1, (2, 3)), (10, 5, 2, 33, (1, 2, 9))):
+        _check_copy_to_dests(vname, T_in, groups, tpd, B, empty)
+
+
+def _check_copy_to_dests(vname, T_in, groups, tpd, B, empty):
+    import torch
+    from fbgemm_ascend_b200 import cabi
+
+    rng = _rng("to-dests", vname, T_in, tpd, B)
     permute = rng.permutation(T_in).astype(np.int32)
     lengths = rng.integers(0, 10, (T_in, B)).astype(np.int64)
+    lengths[list(empty)] = 0                      # whole tables without values, also at the edges of a destination
     total = int(lengths.sum())
     vdt = _torch_dtype(vname)
     values = torch.arange(total, dtype=torch.float32).to(vdt) if vdt.is_floating_point else torch.arange(total, dtype=vdt)
@@ -154,7 +162,7 @@ def test_permute_copy_to_several_destinations(vname):
     out_len = cabi.permute_2d_sparse_offsets(perm_d, len_d, scratch, status)
     assert np.array_equal(out_len.cpu().numpy(), want_len)
     group_sizes = [int(bounds[(g + 1) * tpd] - bounds[g * tpd]) for g in range(groups)]
-    for cap, overflow in ((max(group_sizes) + 8, False), (min(group_sizes) // 2, True)):
+    for cap, overflow in ((max(group_sizes) + 8, False), (max(group_sizes) // 2, True)):
         pad = 64
         bufs = [torch.full((cap + pad,), 7, dtype=vdt, device=dev) for _ in range(groups)]
         bases = torch.tensor([b.data_ptr() for b in bufs], dtype=torch.int64, device=dev)
