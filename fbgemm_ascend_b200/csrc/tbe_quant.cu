@@ -364,21 +364,24 @@ quantize_nbit_kernel(const float* __restrict__ in, int64_t N, int64_t D, uint8_t
         for (int64_t c = 4 + pbytes + k; c < out_stride; c += LPR) o[c] = 0;
 }
 
-// The common 4-bit shapes, batched like the 8-bit ones: fp32 rows of D = 8 * n <= 256 elements, 16-byte aligned input
-// and output.  LPR lanes share a row (8 elements = one 32-bit word of codes per lane), 32 / LPR rows per pass, four
-// passes of loads in flight per warp; the warp builds the image of its 4 * 32 / LPR output rows -- contiguous in the
-// output -- in shared memory and writes it as whole 16-byte pieces.  Same arithmetic as quantize_nbit_kernel<.., 4, ..>,
-// hence the same bytes.
+// The common 4- and 2-bit shapes, batched like the 8-bit ones: fp32 rows of D = n * 32 / BITS elements (one 32-bit word
+// of codes per lane: 8 or 16 elements), 16-byte aligned input and output.  LPR lanes share a row, 32 / LPR rows per
+// pass, PASSES passes of loads in flight per warp; the warp builds the image of its PASSES * 32 / LPR output rows --
+// contiguous in the output -- in shared memory and writes it as whole 16-byte pieces.  Same arithmetic as
+// quantize_nbit_kernel, hence the same bytes.
 constexpr int kStaged4Bytes = 1280;
-template <bool TABLE, int LPR>
+template <bool TABLE, int LPR, int BITS>
 __global__ void __launch_bounds__(kThreads)
-quantize_4bit_batched_kernel(const float* __restrict__ in, int64_t N, int64_t D, uint8_t* __restrict__ out, int64_t out_stride)
+quantize_nbit_batched_kernel(const float* __restrict__ in, int64_t N, int64_t D, uint8_t* __restrict__ out, int64_t out_stride)
 {
-    constexpr int RPP = 32 / LPR, PASSES = 4, R = RPP * PASSES;
+    constexpr int EL = 32 / BITS;                 // elements per lane and row: one word of codes
+    constexpr int VL = EL / 4;                    // float4 per lane and row
+    constexpr int QMAX = (1 << BITS) - 1;
+    constexpr int RPP = 32 / LPR, PASSES = (BITS == 4) ? 4 : 2, R = RPP * PASSES;
     __shared__ __align__(16) uint8_t staged[kThreads / 32][kStaged4Bytes];
     uint8_t* img = staged[threadIdx.x >> 5];
     const int lane = threadIdx.x & 31, k = lane % LPR, g = lane / LPR;
-    const int nunits = static_cast<int>(D / 8), pbytes = static_cast<int>(D / 2), stride = static_cast<int>(out_stride);
+    const int nunits = static_cast<int>(D / EL), pbytes = static_cast<int>(D * BITS / 8), stride = static_cast<int>(out_stride);
     const bool active = k < nunits;
     const int64_t nwarps = static_cast<int64_t>(gridDim.x) * (kThreads / 32);
     const int64_t warp = static_cast<int64_t>(blockIdx.x) * (kThreads / 32) + (threadIdx.x >> 5);
@@ -389,13 +392,13 @@ quantize_4bit_batched_kernel(const float* __restrict__ in, int64_t N, int64_t D,
             for (int c = 4 + pbytes + lane; c < stride; c += 32) img[r * stride + c] = 0;
     }
     for (int64_t r0 = warp * R; r0 < N; r0 += nwarps * R) {
-        float4 a[PASSES], b[PASSES];
+        float4 x4[PASSES][VL];
 #pragma unroll
         for (int p = 0; p < PASSES; ++p) {
             const int64_t row = r0 + p * RPP + g;
             if (row < N && active) {
-                a[p] = __ldg(in4 + row * (2 * nunits) + 2 * k);
-                b[p] = __ldg(in4 + row * (2 * nunits) + 2 * k + 1);
+#pragma unroll
+                for (int v = 0; v < VL; ++v) x4[p][v] = __ldg(in4 + row * (VL * nunits) + VL * k + v);
             }
         }
 #pragma unroll
@@ -404,8 +407,11 @@ quantize_4bit_batched_kernel(const float* __restrict__ in, int64_t N, int64_t D,
             const bool live = row < N && active;
             float mn = __int_as_float(0x7f800000), mx = __int_as_float(0xff800000);
             if (live) {
-                mn = fminf(fminf(fminf(a[p].x, a[p].y), fminf(a[p].z, a[p].w)), fminf(fminf(b[p].x, b[p].y), fminf(b[p].z, b[p].w)));
-                mx = fmaxf(fmaxf(fmaxf(a[p].x, a[p].y), fmaxf(a[p].z, a[p].w)), fmaxf(fmaxf(b[p].x, b[p].y), fmaxf(b[p].z, b[p].w)));
+#pragma unroll
+                for (int v = 0; v < VL; ++v) {
+                    mn = fminf(mn, fminf(fminf(x4[p][v].x, x4[p][v].y), fminf(x4[p][v].z, x4[p][v].w)));
+                    mx = fmaxf(mx, fmaxf(fmaxf(x4[p][v].x, x4[p][v].y), fmaxf(x4[p][v].z, x4[p][v].w)));
+                }
             }
 #pragma unroll
             for (int d = LPR / 2; d > 0; d >>= 1) {
@@ -416,7 +422,7 @@ quantize_4bit_batched_kernel(const float* __restrict__ in, int64_t N, int64_t D,
             const __half bias_h = __float2half_rn(mn);
             const float bias = __half2float(bias_h);
             const float range = __fsub_rn(mx, bias);
-            float scale = (range == 0.0f) ? 1.0f : __fdiv_rn(range, 15.0f);
+            float scale = (range == 0.0f) ? 1.0f : __fdiv_rn(range, static_cast<float>(QMAX));
             __half scale_h = __float2half_rn(scale);
             scale = __half2float(scale_h);
             if (scale == 0.0f) {
@@ -428,13 +434,16 @@ quantize_4bit_batched_kernel(const float* __restrict__ in, int64_t N, int64_t D,
                 scale_h = __float2half_rn(1.0f);
                 inv = 1.0f;
             }
-            const float x[8] = {a[p].x, a[p].y, a[p].z, a[p].w, b[p].x, b[p].y, b[p].z, b[p].w};
             uint32_t word = 0;
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                int q = __float2int_rn(__fmul_rn(__fsub_rn(x[j], bias), inv));
-                q = max(0, min(15, q));
-                word |= static_cast<uint32_t>(q) << (4 * j);
+            for (int v = 0; v < VL; ++v) {
+                const float x[4] = {x4[p][v].x, x4[p][v].y, x4[p][v].z, x4[p][v].w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    int q = __float2int_rn(__fmul_rn(__fsub_rn(x[j], bias), inv));
+                    q = max(0, min(QMAX, q));
+                    word |= static_cast<uint32_t>(q) << (BITS * (4 * v + j));
+                }
             }
             uint8_t* o = img + (p * RPP + g) * stride;
             *reinterpret_cast<uint32_t*>(o + (TABLE ? 4 : 0) + 4 * k) = word;
@@ -445,7 +454,8 @@ quantize_4bit_batched_kernel(const float* __restrict__ in, int64_t N, int64_t D,
         __syncwarp();
         const int64_t rows = (N - r0 < R) ? N - r0 : R;
         const int bytes = static_cast<int>(rows) * stride;
-        uint8_t* dst = out + r0 * out_stride;                  // 16-byte aligned: r0 is a multiple of R >= 4, the stride of 4
+        uint8_t* dst = out + r0 * out_stride;                  // 16-byte aligned: r0 is a multiple of R >= 4 (or 2 rows of a
+                                                               // stride that is a multiple of 8), the stride of 4
         for (int c = lane * 16; c + 16 <= bytes; c += 32 * 16)
             *reinterpret_cast<uint4*>(dst + c) = *reinterpret_cast<const uint4*>(img + c);
         for (int c = (bytes & ~15) + lane; c < bytes; c += 32) dst[c] = img[c];
@@ -632,21 +642,33 @@ int quantize_8bit_impl(const void* input, int in_is_half, int64_t N, int64_t D, 
 int quantize_nbit_impl(int bit_rate, const float* input, int64_t N, int64_t D, uint8_t* out, int64_t out_stride,
                        bool table, cudaStream_t s)
 {
-    // fp32 rows of the common 4-bit widths take the batched kernel
-    if (bit_rate == 4 && D >= 32 && D <= 256 && D % 8 == 0 && N > 0 && (reinterpret_cast<uintptr_t>(input) & 15) == 0 &&
-        (reinterpret_cast<uintptr_t>(out) & 15) == 0 && out_stride % 4 == 0 && out_stride >= D / 2 + 4) {
-        const int lanes = (D <= 32) ? 4 : (D <= 64) ? 8 : (D <= 128) ? 16 : 32;
-        const int64_t rows_per_warp = 4 * (32 / lanes);
-        if (rows_per_warp * out_stride <= kStaged4Bytes) {
+    // fp32 rows of the common widths take the batched kernel
+    const int el = 32 / bit_rate;                                  // elements per 32-bit word of codes
+    if ((bit_rate == 4 || bit_rate == 2) && D >= 4 * el && D <= 32 * el && D % el == 0 && N > 0 &&
+        (reinterpret_cast<uintptr_t>(input) & 15) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0 && out_stride % 4 == 0 &&
+        out_stride >= D * bit_rate / 8 + 4) {
+        const int64_t units = D / el;
+        const int lanes = (units <= 4) ? 4 : (units <= 8) ? 8 : (units <= 16) ? 16 : 32;
+        const int64_t rows_per_warp = (bit_rate == 4 ? 4 : 2) * (32 / lanes);
+        // the rows of a warp and step must start on a 16-byte boundary and fit the staging area
+        if (rows_per_warp * out_stride <= kStaged4Bytes && (rows_per_warp * out_stride) % 16 == 0) {
             const int64_t groups = (N + rows_per_warp - 1) / rows_per_warp;
             const int64_t want = (groups + kThreads / 32 - 1) / (kThreads / 32);
             const int64_t cap = static_cast<int64_t>(sm_count()) * 8;
             const unsigned blocks = static_cast<unsigned>(want < cap ? want : cap);
-#define TBE_Q4B(TAB, LANES) quantize_4bit_batched_kernel<TAB, LANES><<<blocks, kThreads, 0, s>>>(input, N, D, out, out_stride)
-            if (table) { if (lanes == 4) TBE_Q4B(true, 4); else if (lanes == 8) TBE_Q4B(true, 8); else if (lanes == 16) TBE_Q4B(true, 16); else TBE_Q4B(true, 32); }
-            else { if (lanes == 4) TBE_Q4B(false, 4); else if (lanes == 8) TBE_Q4B(false, 8); else if (lanes == 16) TBE_Q4B(false, 16); else TBE_Q4B(false, 32); }
-#undef TBE_Q4B
-            return check_launch("quantize_4bit_batched_kernel");
+#define TBE_QNB(TAB, LANES, BITS) quantize_nbit_batched_kernel<TAB, LANES, BITS><<<blocks, kThreads, 0, s>>>(input, N, D, out, out_stride)
+#define TBE_QNB_LANES(TAB, BITS)                                      \
+    do {                                                              \
+        if (lanes == 4) TBE_QNB(TAB, 4, BITS);                        \
+        else if (lanes == 8) TBE_QNB(TAB, 8, BITS);                   \
+        else if (lanes == 16) TBE_QNB(TAB, 16, BITS);                 \
+        else TBE_QNB(TAB, 32, BITS);                                  \
+    } while (0)
+            if (bit_rate == 4) { if (table) TBE_QNB_LANES(true, 4); else TBE_QNB_LANES(false, 4); }
+            else { if (table) TBE_QNB_LANES(true, 2); else TBE_QNB_LANES(false, 2); }
+#undef TBE_QNB_LANES
+#undef TBE_QNB
+            return check_launch("quantize_nbit_batched_kernel");
         }
     }
     const int lpr = (D <= 128) ? 8 : 32;
