@@ -225,6 +225,86 @@ quantize_8bit_batched_kernel(const float* __restrict__ in, int64_t N, int64_t D,
     }
 }
 
+// The same for D = 8 * n <= 256 with EIGHT elements per lane: LPR lanes share a row, 32 / LPR rows per pass, four passes of
+// loads in flight, so the per-row work that does not depend on the width (the two divisions, the header, the
+// reduction, the bounds checks) is issued once for 32 / LPR rows instead of once per row -- the kernel is bound by
+// instruction issue, not by memory.  The warp's 4 * 32 / LPR output rows are staged in shared memory and leave as whole
+// 16-byte pieces.  Same arithmetic, hence the same bytes.
+constexpr int kStaged8Bytes = 2304;      // 16 rows of 144 bytes
+template <bool TABLE, int LPR>
+__global__ void __launch_bounds__(kThreads)
+quantize_8bit_wide_kernel(const float* __restrict__ in, int64_t N, int64_t D, uint8_t* __restrict__ out, int64_t out_stride)
+{
+    constexpr int RPP = 32 / LPR, PASSES = 4, R = RPP * PASSES;
+    __shared__ __align__(16) uint8_t staged[kThreads / 32][kStaged8Bytes];
+    uint8_t* img = staged[threadIdx.x >> 5];
+    const int lane = threadIdx.x & 31, k = lane % LPR, g = lane / LPR;
+    const int nunits = static_cast<int>(D / 8), stride = static_cast<int>(out_stride), Di = static_cast<int>(D);
+    const bool active = k < nunits;
+    const int64_t nwarps = static_cast<int64_t>(gridDim.x) * (kThreads / 32);
+    const int64_t warp = static_cast<int64_t>(blockIdx.x) * (kThreads / 32) + (threadIdx.x >> 5);
+    const float4* in4 = reinterpret_cast<const float4*>(in);
+    if (TABLE) {
+        for (int r = 0; r < R; ++r)
+            for (int c = 4 + Di + lane; c < stride; c += 32) img[r * stride + c] = 0;     // padding: cleared once
+    }
+    for (int64_t r0 = warp * R; r0 < N; r0 += nwarps * R) {
+        float4 a[PASSES], b[PASSES];
+#pragma unroll
+        for (int p = 0; p < PASSES; ++p) {
+            const int64_t row = r0 + p * RPP + g;
+            if (row < N && active) {
+                a[p] = __ldg(in4 + row * (2 * nunits) + 2 * k);
+                b[p] = __ldg(in4 + row * (2 * nunits) + 2 * k + 1);
+            }
+        }
+#pragma unroll
+        for (int p = 0; p < PASSES; ++p) {
+            const int64_t row = r0 + p * RPP + g;
+            const bool live = row < N && active;
+            float mn = __int_as_float(0x7f800000), mx = __int_as_float(0xff800000);
+            if (live) {
+                mn = fminf(fminf(fminf(a[p].x, a[p].y), fminf(a[p].z, a[p].w)), fminf(fminf(b[p].x, b[p].y), fminf(b[p].z, b[p].w)));
+                mx = fmaxf(fmaxf(fmaxf(a[p].x, a[p].y), fmaxf(a[p].z, a[p].w)), fmaxf(fmaxf(b[p].x, b[p].y), fmaxf(b[p].z, b[p].w)));
+            }
+#pragma unroll
+            for (int d = LPR / 2; d > 0; d >>= 1) {
+                mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, d));
+                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, d));
+            }
+            if (!live) continue;
+            const float range = mx - mn;
+            const float scale = __fdiv_rn(range, 255.0f);
+            const float inv = __fdiv_rn(255.0f, __fadd_rn(range, 1e-8f));
+            const float x[8] = {a[p].x, a[p].y, a[p].z, a[p].w, b[p].x, b[p].y, b[p].z, b[p].w};
+            uint32_t w[2] = {0u, 0u};
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+                w[j >> 2] |= (static_cast<uint32_t>(__float2int_rn(__fmul_rn(__fsub_rn(x[j], mn), inv))) & 0xffu) << (8 * (j & 3));
+            uint8_t* o = img + (p * RPP + g) * stride;
+            uint8_t* codes = (TABLE ? o + 4 : o) + 8 * k;        // 4-byte aligned (table rows) or 8-byte aligned
+            *reinterpret_cast<uint32_t*>(codes) = w[0];
+            *reinterpret_cast<uint32_t*>(codes + 4) = w[1];
+            if (k == 0) {
+                if (TABLE) {
+                    *reinterpret_cast<uint32_t*>(o) = (f32_to_f16_bits(scale) & 0xffffu) | (f32_to_f16_bits(mn) << 16);
+                } else {
+                    *reinterpret_cast<uint32_t*>(o + Di) = __float_as_uint(scale);
+                    *reinterpret_cast<uint32_t*>(o + Di + 4) = __float_as_uint(mn);
+                }
+            }
+        }
+        __syncwarp();
+        const int64_t rows = (N - r0 < R) ? N - r0 : R;
+        const int bytes = static_cast<int>(rows) * stride;
+        uint8_t* dst = out + r0 * out_stride;                  // 16-byte aligned: r0 is a multiple of R >= 4, the stride of 4
+        for (int c = lane * 16; c + 16 <= bytes; c += 32 * 16)
+            *reinterpret_cast<uint4*>(dst + c) = *reinterpret_cast<const uint4*>(img + c);
+        for (int c = (bytes & ~15) + lane; c < bytes; c += 32) dst[c] = img[c];
+        __syncwarp();
+    }
+}
+
 // 8-bit rows back to fp32, batched the same way: D = 4 * n <= 512, ROWS rows per warp in flight.
 template <int VPL, int ROWS>
 __global__ void __launch_bounds__(kThreads)
@@ -617,6 +697,22 @@ int quantize_8bit_impl(const void* input, int in_is_half, int64_t N, int64_t D, 
         const int64_t cap = static_cast<int64_t>(sm_count()) * 8;
         const unsigned blocks = static_cast<unsigned>(want < cap ? want : cap);
 #define TBE_Q8B(TAB, VPL, ROWS) quantize_8bit_batched_kernel<TAB, VPL, ROWS><<<blocks, kThreads, 0, s>>>(x, N, D, out, out_stride)
+        // D a multiple of 8 up to 256, 16-byte aligned output: eight elements per lane, several rows per pass
+        if (D % 8 == 0 && D <= 256 && (reinterpret_cast<uintptr_t>(out) & 15) == 0 && out_stride >= D + (table ? 4 : 8)) {
+            const int64_t units = D / 8;
+            const int lanes = (units <= 4) ? 4 : (units <= 8) ? 8 : (units <= 16) ? 16 : 32;
+            const int64_t rows_per_warp = 4 * (32 / lanes);
+            if (rows_per_warp * out_stride <= kStaged8Bytes) {
+                const int64_t groups8 = (N + rows_per_warp - 1) / rows_per_warp;
+                const int64_t want8 = (groups8 + kThreads / 32 - 1) / (kThreads / 32);
+                const unsigned blocks8 = static_cast<unsigned>(want8 < cap ? want8 : cap);
+#define TBE_Q8W(TAB, LANES) quantize_8bit_wide_kernel<TAB, LANES><<<blocks8, kThreads, 0, s>>>(x, N, D, out, out_stride)
+                if (table) { if (lanes == 4) TBE_Q8W(true, 4); else if (lanes == 8) TBE_Q8W(true, 8); else if (lanes == 16) TBE_Q8W(true, 16); else TBE_Q8W(true, 32); }
+                else { if (lanes == 4) TBE_Q8W(false, 4); else if (lanes == 8) TBE_Q8W(false, 8); else if (lanes == 16) TBE_Q8W(false, 16); else TBE_Q8W(false, 32); }
+#undef TBE_Q8W
+                return check_launch("quantize_8bit_wide_kernel");
+            }
+        }
         const bool staged = D <= 128 && out_stride <= kStagedStride && (reinterpret_cast<uintptr_t>(out) & 15) == 0;
         if (staged) {
             if (table) quantize_8bit_batched_kernel<true, 1, 4, true><<<blocks, kThreads, 0, s>>>(x, N, D, out, out_stride);
