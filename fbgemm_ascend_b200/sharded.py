@@ -316,11 +316,28 @@ class FeatureMajorInputDist:
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
         self._scratch = torch.empty(cabi.permute_2d_sparse_scratch_elems(len(p.dims), len(p.dims)), dtype=torch.int64, device=self.device)
         # second permute over world x (T_loc + 1) segments: the extra one per source stands for the unused rest of its slot
-        t32 = lambda v: torch.tensor(v, dtype=torch.int32, device=self.device)
-        self._to_table_major_slots = t32([s * (self.T_loc + 1) + j for j in range(self.T_loc) for s in range(w)])
+        self._to_table_major_slots = torch.tensor(self.slot_permute_list(w, self.T_loc), dtype=torch.int32, device=self.device)
         self._step = 0
         torch.cuda.synchronize(self.device)
         dist.barrier(group=self.group)
+
+    @staticmethod
+    def slot_permute_list(world: int, T_loc: int) -> List[int]:
+        """Permute list of the second ``permute_2D_sparse_data`` when the values sit in ``world`` slots: slot ``s`` is
+        ``T_loc`` segments (source ``s``'s values for the local tables) followed by one more for the unused rest of the
+        slot, which the list leaves out; the result is (local table, source rank) order."""
+        return [s * (T_loc + 1) + j for j in range(T_loc) for s in range(world)]
+
+    @staticmethod
+    def slot_segment_lengths(len_recv: torch.Tensor, recv_counts: torch.Tensor, cap: int) -> torch.Tensor:
+        """``len_recv`` [world, T_loc, B_loc] -> [world, T_loc + 1, B_loc]: every slot gets one more "table" whose first
+        length is the unused rest of the slot (``cap`` minus what the source sent), so that the running sum of all
+        lengths gives every segment's position inside the ``world * cap`` receive buffer."""
+        w, T_loc, B_loc = len_recv.shape
+        ext = torch.zeros((w, T_loc + 1, B_loc), dtype=len_recv.dtype, device=len_recv.device)
+        ext[:, :T_loc] = len_recv
+        ext[:, T_loc, 0] = cap - recv_counts.to(len_recv.dtype)
+        return ext
 
     def check_status(self) -> int:
         """0, or bit 2 (a slot was too small: values were dropped) / bit 16 (a peer's step flag did not arrive in time)."""
@@ -356,9 +373,7 @@ class FeatureMajorInputDist:
         cabi.wait_flags(self._flags[k], w, value, self.max_polls, self.status)
         self._mark("wait_for_peer_stores")
         # 3. slots -> table-major: every source's slot is its T_loc segments plus one segment of unused space
-        len_ext = torch.zeros((w, T_loc + 1, B_loc), dtype=len_recv.dtype, device=self.device)
-        len_ext[:, :T_loc] = len_recv.view(w, T_loc, B_loc)
-        len_ext[:, T_loc, 0] = cap - recv_counts
+        len_ext = self.slot_segment_lengths(len_recv.view(w, T_loc, B_loc), recv_counts, cap)
         len_tm, idx_tm, _ = self.permute_fn(self._to_table_major_slots, len_ext.view(w * (T_loc + 1), B_loc), self._recv[k].view(-1), None, total)
         self._mark("permute_to_table_major")
         offsets = self.cumsum_fn(len_tm.reshape(-1)).to(self.index_dtype)

@@ -214,3 +214,38 @@ def test_feature_major_input_dist_one_rank():
     l_loc, idx_loc = _local_request(c, 0, 1)
     idx_tm, offs_tm, _ = ind(torch.from_numpy(l_loc), torch.from_numpy(idx_loc))
     assert np.array_equal(idx_tm.numpy(), c.indices) and np.array_equal(offs_tm.numpy(), c.offsets)
+
+
+def test_slot_layout_of_the_peer_store_exchange():
+    """The host logic of ``exchange="direct"`` without GPUs: every rank permutes its request by owner and "stores" owner
+    r's part into slot `rank` of r's receive buffer (here: numpy arrays standing for the peers' memory); the second
+    permute, over the slots' segments plus one segment of unused space per slot, must give the owner the table-major
+    request of the global batch for its tables."""
+    from fbgemm_ascend_b200.sharded import FeatureMajorInputDist, ShardPlan
+    c, dims, tys, order = _global_case()
+    world, B = 2, c.B
+    Bl = B // world
+    plans = [ShardPlan(world=world, rank=r, dims=dims, feature_order=order, global_batch=B) for r in range(world)]
+    T_loc = len(plans[0].local_tables)
+    cap = 16 * ((max(c.indices.size, 1) + 15) // 16)
+    recv = [np.full((world, cap), -7, dtype=np.int64) for _ in range(world)]            # receive buffer of every owner
+    len_recv = [np.zeros((world, T_loc, Bl), dtype=np.int64) for _ in range(world)]
+    for s in range(world):                                                             # what rank s does in step 1
+        l_loc, idx_loc = _local_request(c, s, world)
+        by_owner = np.asarray(plans[s].exchanged_order, dtype=np.int32)
+        l_by, v_by, _ = O.permute_2d_sparse_data(by_owner, l_loc, idx_loc, None)
+        seg = l_by.reshape(world, -1).sum(1)
+        start = np.concatenate([[0], np.cumsum(seg)])
+        for r in range(world):
+            recv[r][s, :seg[r]] = v_by[start[r]:start[r + 1]]                          # the peer store into slot s of owner r
+            len_recv[r][s] = l_by[r * T_loc:(r + 1) * T_loc]                           # the lengths all-to-all
+    offs = c.offsets
+    for r in range(world):                                                             # what owner r does in step 3
+        counts = torch.from_numpy(len_recv[r].reshape(world, -1).sum(1))
+        ext = FeatureMajorInputDist.slot_segment_lengths(torch.from_numpy(len_recv[r]), counts, cap).numpy()
+        perm = np.asarray(FeatureMajorInputDist.slot_permute_list(world, T_loc), dtype=np.int32)
+        l_tm, v_tm, _ = O.permute_2d_sparse_data(perm, ext.reshape(world * (T_loc + 1), Bl), recv[r].reshape(-1), None)
+        want_idx = np.concatenate([c.indices[offs[t * B]:offs[(t + 1) * B]] for t in plans[r].local_tables])
+        want_len = np.concatenate([np.diff(offs[t * B:(t + 1) * B + 1]) for t in plans[r].local_tables])
+        assert np.array_equal(v_tm, want_idx)
+        assert np.array_equal(l_tm.reshape(-1), want_len)
