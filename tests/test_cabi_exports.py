@@ -50,6 +50,15 @@ def test_argument_validation_without_gpu():
     assert "elem_bytes" in cabi.last_error()
     assert lib.tbe_b200_quantize_nbit_rowwise_sbhalf(3, None, 0, 0, None, None) == -2
     assert lib.tbe_b200_quantize_to_table_rows(6, None, 0, 0, 0, None, None) == -2
+    # producers of the lookup's inputs and the step flags
+    assert lib.tbe_b200_complete_cumsum(None, -1, 64, None, None, 0, None) == -1
+    assert lib.tbe_b200_complete_cumsum(None, 4, 16, None, None, 0, None) == -1 and "index_bits" in cabi.last_error()
+    assert lib.tbe_b200_complete_cumsum_scratch_bytes(8192) == 0 and lib.tbe_b200_complete_cumsum_scratch_bytes(8193) == 16 + 2 * 16
+    assert lib.tbe_b200_permute_2d_sparse_copy_to_dests(None, 6, 6, None, 8, None, 4, 10, 10, None, None, None) == -1
+    assert "multiple of tables_per_dest" in cabi.last_error()
+    assert lib.tbe_b200_permute_2d_sparse_copy_to_dests(None, 6, 6, None, 8, None, 3, 10, 10, None, None, None) == -1
+    assert "NULL" in cabi.last_error()
+    assert lib.tbe_b200_wait_flags(None, 2, 1, 0, None, None) != 0
 
 
 def test_operators_registered_and_cpu_tensors_rejected():
