@@ -7,7 +7,7 @@ column remap, error flag) and for tests that exercise the boundary directly.
 from __future__ import annotations
 
 import ctypes as C
-from typing import Optional, Sequence
+from typing import Optional
 
 import torch
 

@@ -27,7 +27,7 @@ from __future__ import annotations
 
 from dataclasses import dataclass
 from itertools import accumulate
-from typing import Callable, List, Optional, Sequence
+from typing import Callable, List, Optional
 
 import torch
 import torch.distributed as dist

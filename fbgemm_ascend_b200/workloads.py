@@ -14,7 +14,7 @@ No public dataset is involved; these generators are the benchmark inputs.
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import Callable, Dict, List, Optional, Sequence, Tuple
+from typing import Callable, Dict, List, Optional, Sequence
 
 import torch
 

@@ -12,7 +12,7 @@ Used by ``tests/`` and by the benchmark's verification step; never by the GPU pa
 """
 from __future__ import annotations
 
-from typing import Dict, Optional
+from typing import Dict
 
 import numpy as np
 

@@ -2,7 +2,6 @@
 accounting."""
 import inspect
 
-import numpy as np
 import pytest
 import torch
 
